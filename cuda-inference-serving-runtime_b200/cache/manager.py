@@ -34,7 +34,7 @@ from .pages import OutOfPages, PagePool
 class PagedBinding:
     """What a paged mixer sees of the cache for one run entry."""
     k: torch.Tensor              # [pages, kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor              # the same tensor as k in a group with one plane
     block_table: torch.Tensor    # [slots, width] int32 on the device
     page_size: int
     write: bool                  # False: the entry reads another entry's pages
@@ -65,8 +65,8 @@ class PageGroup:
         self.storage = None
         self.device_table = None
         if device is not None:
-            # [entries, key|value, pages, kv_heads, page_size, head_dim]
-            self.storage = torch.zeros((len(entries), 2, n_pages, use.kv_heads, page_size, use.head_dim), dtype=dtype,
+            # [entries, key|value, pages, kv_heads, page_size, head_dim]; one plane where a row serves as both
+            self.storage = torch.zeros((len(entries), use.planes, n_pages, use.kv_heads, page_size, use.head_dim), dtype=dtype,
                                        device=device)
             self.device_table = torch.full((max_slots + 1, width), -1, dtype=torch.int32, device=device)   # last row: the null slot
         self.host_table = np.full((max_slots, width), -1, dtype=np.int32)
@@ -293,7 +293,7 @@ class CacheManager:
         if kind == "pages":
             g = self.page_groups[gi]
             e = g.entry_slot[source]
-            return PagedBinding(g.storage[e, 0], g.storage[e, 1], g.device_table, g.page_size,
+            return PagedBinding(g.storage[e, 0], g.storage[e, g.use.planes - 1], g.device_table, g.page_size,
                                 write=reads_from is None, window=g.use.window)
         g = self.state_groups[gi]
         return StateBinding(g.storage[g.entry_slot[source]])

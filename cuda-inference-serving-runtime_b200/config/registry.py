@@ -31,8 +31,10 @@ def register_architecture(name: str, config_class: Any, model_types: tuple = ())
 
 
 def architecture_for(raw: Mapping[str, Any]) -> Architecture:
-    """Pick the architecture by `architectures[0]`, else by `model_type`."""
-    names = raw.get("architectures") or []
+    """Pick the architecture by `architectures[0]` (or the single name under `architecture`), else by `model_type`."""
+    names = list(raw.get("architectures") or [])
+    if isinstance(raw.get("architecture"), str):
+        names.append(raw["architecture"])
     for name in names:
         if name in ARCHITECTURES:
             return ARCHITECTURES[name]

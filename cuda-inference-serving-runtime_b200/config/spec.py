@@ -25,7 +25,9 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a mixer and a feed-forward, each with its norm, and how they are arranged.
+    """One layer: a mixer and a feed-forward, each with its norm, and how they are arranged.  A layer without a
+    feed-forward has `feed_forward` and `feed_forward_norm` None (arrangements that allow it say so).  `extras` are
+    further parts of the arrangement by slot name (per-channel scales of the two outputs, for one).
 
     `names` maps the four slots to the sub-prefix their tensors carry in the
     checkpoint below `prefix` (for Llama: mixer -> "self_attn.", ...).
@@ -33,10 +35,11 @@ class LayerSpec:
     prefix: str
     mixer: PartSpec
     mixer_norm: PartSpec
-    feed_forward: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward: Optional[PartSpec]
+    feed_forward_norm: Optional[PartSpec]
     arrangement: str = "pre_norm"
     names: Mapping[str, str] = field(default_factory=dict)
+    extras: Mapping[str, PartSpec] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -45,10 +48,12 @@ class RunEntry:
 
     `layer` indexes `ModelSpec.layers`; naming a layer twice runs its weights
     twice.  Each entry owns a cache of its own unless `cache_of` names an earlier
-    entry, whose cache it then reads without writing.
+    entry, whose cache it then reads without writing.  `pass_step` t: row t of the model's per-pass vectors
+    (`ModelSpec.pass_steps`) is added to the residual stream right before this entry runs.
     """
     layer: int
     cache_of: Optional[int] = None
+    pass_step: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -56,7 +61,8 @@ class CacheUse:
     """What a mixer needs from the cache manager.
 
     kind "pages": keys and values in pages ([kv_heads, page, head_dim] per page);
-    `window` None keeps every key, an integer keeps the last `window` of them.
+    `window` None keeps every key, an integer keeps the last `window` of them.  `planes` 2: a key plane and a value
+    plane; 1: one plane of rows that serve as both (a latent from which keys and values are derived).
     kind "state": a fixed-size tensor per request of `state_shape`/`state_dtype`.
     kind "none": nothing.
     """
@@ -66,9 +72,10 @@ class CacheUse:
     window: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
     state_dtype: str = "float32"
+    planes: int = 2
 
     def group_key(self) -> tuple:
-        return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shape, self.state_dtype)
+        return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shape, self.state_dtype, self.planes)
 
 
 @dataclass(frozen=True)
@@ -85,6 +92,8 @@ class ModelSpec:
     head: PartSpec
     head_prefix: str
     eos_token_ids: Tuple[int, ...] = ()
+    pass_steps: Optional[PartSpec] = None        # per-pass vectors added to the stream where a run entry names a row
+    pass_steps_prefix: str = ""
 
     def validate(self) -> None:
         if not self.layers or not self.run:
@@ -92,6 +101,8 @@ class ModelSpec:
         for i, entry in enumerate(self.run):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"run entry {i} names layer {entry.layer}, which does not exist")
+            if entry.pass_step is not None and self.pass_steps is None:
+                raise ValueError(f"run entry {i} names a per-pass vector, but the model has none")
             if entry.cache_of is not None:
                 if not 0 <= entry.cache_of < i:
                     raise ValueError(f"run entry {i} reads the cache of entry {entry.cache_of}, which must run earlier")

@@ -15,7 +15,7 @@ CISR_EXPORT void cisr_elementwise_set_pdl(int on) { g_pdl = on != 0; }
 // ---------------------------------------------------------------- embedding
 template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int hidden, int vocab) {
+                                 float* __restrict__ out, int hidden, int vocab, float scale) {
     CISR_TRACE_SCOPE(TRACE_EMBEDDING);
     // Under programmatic dependent launch the kernels after this one may start (and fetch their weights) while it runs.
     // It waits for the kernel before it although it reads nothing of it: a later kernel's wait on this one then also
@@ -28,25 +28,27 @@ __global__ void embedding_kernel(const TT* __restrict__ table, const int* __rest
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // host validates; clamp keeps a bad id from reading outside
     const TT* src = table + (size_t)id * hidden;
     float* dst = out + (size_t)row * hidden;
-    for (int d = threadIdx.x; d < hidden; d += blockDim.x) dst[d] = to_float(src[d]);
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) dst[d] = to_float(src[d]) * scale;   // scale 1 leaves the value as stored
 }
 
 CISR_EXPORT int cisr_embedding(const void* table, int table_dtype, const int* ids, float* out, int tokens,
-                               int hidden, int vocab, void* stream) {
+                               int hidden, int vocab, float scale, void* stream) {
     if (tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == CISR_BF16)
-        return launch_kernel(embedding_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, s, g_pdl, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
-    return launch_kernel(embedding_kernel<float>, dim3(tokens), dim3(128), 0, s, g_pdl, (const float*)table, ids, out, hidden, vocab);
+        return launch_kernel(embedding_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, s, g_pdl, (const __nv_bfloat16*)table, ids, out, hidden, vocab, scale);
+    return launch_kernel(embedding_kernel<float>, dim3(tokens), dim3(128), 0, s, g_pdl, (const float*)table, ids, out, hidden, vocab, scale);
 }
 
 // ---------------------------------------------------------------- residual add + RMSNorm
-// For output row r: src = rows ? rows[r] : r;  v = x[src] + delta[src];  (x[src] = v if write_back)
-// out[r] = v * rsqrt(mean(v^2) + eps) * w.
+// For output row r: src = rows ? rows[r] : r;  v = x[src] + delta[src] * dscale;  (x[src] = v if write_back)
+// out[r] = v * rsqrt(mean(v^2) + eps) * w.  dscale (float, one per channel; null: 1) is a layer scale: the output of a
+// sub-block is multiplied by it on its way into the stream.
 template <typename WT, typename OT>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                    const WT* __restrict__ weight, OT* __restrict__ out,
-                                   const int* __restrict__ rows, int hidden, float eps, int write_back) {
+                                   const int* __restrict__ rows, int hidden, float eps, int write_back,
+                                   const float* __restrict__ dscale) {
     CISR_TRACE_SCOPE(TRACE_ADD_RMSNORM);
     __shared__ float scratch[32];
     const int r = blockIdx.x;
@@ -57,7 +59,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
     float sq = 0.f;
     for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
         float v = xr[d];
-        if (dr) v += dr[d];
+        if (dr) v += dscale ? dr[d] * dscale[d] : dr[d];
         if (write_back && dr) xr[d] = v;
         row_cache[d] = v;
         sq += v * v;
@@ -88,7 +90,8 @@ __device__ __forceinline__ void store4(__nv_bfloat16* o, int d4, float4 v) {
 template <typename WT, typename OT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                        const WT* __restrict__ weight, OT* __restrict__ out,
-                                       const int* __restrict__ rows, int hidden, float eps, int write_back) {
+                                       const int* __restrict__ rows, int hidden, float eps, int write_back,
+                                       const float* __restrict__ dscale) {
     CISR_TRACE_SCOPE(TRACE_ADD_RMSNORM);
     __shared__ float scratch[32];
     extern __shared__ __align__(16) float row_cache[];
@@ -104,7 +107,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __res
     for (int d = threadIdx.x; d < h4; d += blockDim.x) {
         float4 v = xr[d];
         if (dr) {
-            const float4 dv = dr[d];
+            float4 dv = dr[d];
+            if (dscale) { const float4 ds = reinterpret_cast<const float4*>(dscale)[d]; dv.x *= ds.x; dv.y *= ds.y; dv.z *= ds.z; dv.w *= ds.w; }
             v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
             if (write_back) xr[d] = v;
         }
@@ -139,7 +143,8 @@ constexpr int NORM_WARPS = 4;
 template <typename WT, typename OT, int V>
 __global__ void __launch_bounds__(32 * NORM_WARPS)
 add_rmsnorm_warp_kernel(float* __restrict__ x, const float* __restrict__ delta, const WT* __restrict__ weight,
-                        OT* __restrict__ out, const int* __restrict__ rows, int n_rows, int hidden, float eps, int write_back) {
+                        OT* __restrict__ out, const int* __restrict__ rows, int n_rows, int hidden, float eps, int write_back,
+                        const float* __restrict__ dscale) {
     CISR_TRACE_SCOPE(TRACE_ADD_RMSNORM);
     pdl_trigger();
     pdl_wait();          // x and delta come from the kernels before
@@ -162,6 +167,10 @@ add_rmsnorm_warp_kernel(float* __restrict__ x, const float* __restrict__ delta, 
         for (int i = 0; i < V; ++i) {
             const int d = lane + 32 * i;
             dv[i] = d < h4 ? dr[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (dscale && d < h4) {
+                const float4 ds = reinterpret_cast<const float4*>(dscale)[d];
+                dv[i].x *= ds.x; dv[i].y *= ds.y; dv[i].z *= ds.z; dv[i].w *= ds.w;
+            }
         }
 #pragma unroll
         for (int i = 0; i < V; ++i) {
@@ -184,28 +193,28 @@ add_rmsnorm_warp_kernel(float* __restrict__ x, const float* __restrict__ delta, 
 
 template <typename WT, typename OT, int V>
 static int add_rmsnorm_warp_launch(float* x, const float* delta, const void* w, void* out, const int* rows, int n_rows,
-                                   int hidden, float eps, int write_back, cudaStream_t s) {
+                                   int hidden, float eps, int write_back, const float* dscale, cudaStream_t s) {
     return launch_kernel(add_rmsnorm_warp_kernel<WT, OT, V>, dim3((n_rows + NORM_WARPS - 1) / NORM_WARPS), dim3(32 * NORM_WARPS), 0, s,
-                         g_pdl, x, delta, (const WT*)w, (OT*)out, rows, n_rows, hidden, eps, write_back);
+                         g_pdl, x, delta, (const WT*)w, (OT*)out, rows, n_rows, hidden, eps, write_back, dscale);
 }
 
 template <typename WT, typename OT>
 static int add_rmsnorm_launch(float* x, const float* delta, const void* w, void* out, const int* rows, int n_rows,
-                              int hidden, float eps, int write_back, cudaStream_t s) {
+                              int hidden, float eps, int write_back, const float* dscale, cudaStream_t s) {
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) return -2;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<WT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    const bool vec = (hidden & 3) == 0 && !(((uintptr_t)x | (uintptr_t)delta) & 15);
+    const bool vec = (hidden & 3) == 0 && !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)dscale) & 15);
     // rows of up to 2048 floats whose weights and outputs are aligned too: a warp per row
     if (vec && hidden <= 2048 && !(((uintptr_t)w | (uintptr_t)out) & 15) && (hidden * sizeof(OT)) % 16 == 0) {
         const int per_lane = (hidden / 4 + 31) / 32;
-        if (per_lane <= 2) return add_rmsnorm_warp_launch<WT, OT, 2>(x, delta, w, out, rows, n_rows, hidden, eps, write_back, s);
-        if (per_lane <= 5) return add_rmsnorm_warp_launch<WT, OT, 5>(x, delta, w, out, rows, n_rows, hidden, eps, write_back, s);
-        if (per_lane <= 8) return add_rmsnorm_warp_launch<WT, OT, 8>(x, delta, w, out, rows, n_rows, hidden, eps, write_back, s);
-        return add_rmsnorm_warp_launch<WT, OT, 16>(x, delta, w, out, rows, n_rows, hidden, eps, write_back, s);
+        if (per_lane <= 2) return add_rmsnorm_warp_launch<WT, OT, 2>(x, delta, w, out, rows, n_rows, hidden, eps, write_back, dscale, s);
+        if (per_lane <= 5) return add_rmsnorm_warp_launch<WT, OT, 5>(x, delta, w, out, rows, n_rows, hidden, eps, write_back, dscale, s);
+        if (per_lane <= 8) return add_rmsnorm_warp_launch<WT, OT, 8>(x, delta, w, out, rows, n_rows, hidden, eps, write_back, dscale, s);
+        return add_rmsnorm_warp_launch<WT, OT, 16>(x, delta, w, out, rows, n_rows, hidden, eps, write_back, dscale, s);
     }
     if (smem > 48 * 1024 && vec) {
         cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_vec_kernel<WT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -214,26 +223,26 @@ static int add_rmsnorm_launch(float* x, const float* delta, const void* w, void*
     if (vec) {
         const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
         return launch_kernel(add_rmsnorm_vec_kernel<WT, OT>, dim3(n_rows), dim3(threads), smem, s, g_pdl, x, delta, (const WT*)w,
-                             (OT*)out, rows, hidden, eps, write_back);
+                             (OT*)out, rows, hidden, eps, write_back, dscale);
     } else {
         const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-        add_rmsnorm_kernel<WT, OT><<<n_rows, threads, smem, s>>>(x, delta, (const WT*)w, (OT*)out, rows, hidden, eps, write_back);
+        add_rmsnorm_kernel<WT, OT><<<n_rows, threads, smem, s>>>(x, delta, (const WT*)w, (OT*)out, rows, hidden, eps, write_back, dscale);
     }
     return launch_status();
 }
 
 CISR_EXPORT int cisr_add_rmsnorm(float* x, const float* delta, const void* weight, int w_dtype, void* out,
                                  int out_dtype, const int* rows, int n_rows, int hidden, float eps, int write_back,
-                                 void* stream) {
+                                 const float* dscale, void* stream) {
     if (n_rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (w_dtype == CISR_BF16 && out_dtype == CISR_BF16)
-        return add_rmsnorm_launch<__nv_bfloat16, __nv_bfloat16>(x, delta, weight, out, rows, n_rows, hidden, eps, write_back, s);
+        return add_rmsnorm_launch<__nv_bfloat16, __nv_bfloat16>(x, delta, weight, out, rows, n_rows, hidden, eps, write_back, dscale, s);
     if (w_dtype == CISR_F32 && out_dtype == CISR_BF16)
-        return add_rmsnorm_launch<float, __nv_bfloat16>(x, delta, weight, out, rows, n_rows, hidden, eps, write_back, s);
+        return add_rmsnorm_launch<float, __nv_bfloat16>(x, delta, weight, out, rows, n_rows, hidden, eps, write_back, dscale, s);
     if (w_dtype == CISR_BF16 && out_dtype == CISR_F32)
-        return add_rmsnorm_launch<__nv_bfloat16, float>(x, delta, weight, out, rows, n_rows, hidden, eps, write_back, s);
-    return add_rmsnorm_launch<float, float>(x, delta, weight, out, rows, n_rows, hidden, eps, write_back, s);
+        return add_rmsnorm_launch<__nv_bfloat16, float>(x, delta, weight, out, rows, n_rows, hidden, eps, write_back, dscale, s);
+    return add_rmsnorm_launch<float, float>(x, delta, weight, out, rows, n_rows, hidden, eps, write_back, dscale, s);
 }
 
 // ---------------------------------------------------------------- SwiGLU
@@ -360,6 +369,39 @@ CISR_EXPORT int cisr_rope_store(const float* proj, int row_stride, int k_col, in
     else if (q_dtype == CISR_BF16 && cache_dtype == CISR_F32) CISR_ROPE(__nv_bfloat16, float);
     else CISR_ROPE(float, __nv_bfloat16);
 #undef CISR_ROPE
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- stream add and plain scaling
+// x[t, d] += delta[t, d] * dscale[d] + vec[d]: a pending sub-block output (with its layer scale) and a per-pass vector
+// enter the residual stream in one pass over it.  Any of delta, dscale and vec may be null.
+__global__ void stream_add_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ dscale,
+                                  const float* __restrict__ vec, int hidden, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int d = (int)(i % hidden);
+    float v = x[i];
+    if (delta) v += dscale ? delta[i] * dscale[d] : delta[i];
+    if (vec) v += vec[d];
+    x[i] = v;
+}
+
+CISR_EXPORT int cisr_stream_add(float* x, const float* delta, const float* dscale, const float* vec, int tokens, int hidden,
+                                void* stream) {
+    const size_t total = (size_t)tokens * hidden;
+    if (!total) return 0;
+    stream_add_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, delta, dscale, vec, hidden, total);
+    return launch_status();
+}
+
+__global__ void scale_kernel(float* __restrict__ x, float scale, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] *= scale;
+}
+
+CISR_EXPORT int cisr_scale(float* x, long long total, float scale, void* stream) {
+    if (total <= 0) return 0;
+    scale_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, scale, (size_t)total);
     return launch_status();
 }
 

@@ -40,3 +40,24 @@ CISR_EXPORT int cisr_gemm_library(const void* a, const void* w, int dtype, float
                                      CUDA_R_32F, n, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
     return st == CUBLAS_STATUS_SUCCESS ? 0 : -100 - (int)st;
 }
+
+// One product per head in one call: out_b[M, N] = a_b[M, K] * w_b, b = 0 .. batch - 1, where operand b starts
+// `stride` elements after operand b - 1 and rows are `ld` elements apart (heads that lie side by side in one
+// activation row, and a weight matrix stored head by head).  w_b is [N, K] (w_is_nk, the checkpoint's [out, in]
+// layout) or [K, N] (the same matrix used from its other side).  The output takes the operands' type or float.
+CISR_EXPORT int cisr_gemm_library_batched(const void* a, int lda, long long stride_a, const void* w, int ldw,
+                                          long long stride_w, int w_is_nk, int dtype, void* out, int ldo,
+                                          long long stride_o, int out_dtype, int m, int n, int k, int batch, void* stream) {
+    if (m <= 0 || n <= 0 || batch <= 0) return 0;
+    if (!g_handle) return -13;
+    cublasHandle_t h = dtype == CISR_BF16 ? g_handle : g_handle_f32;
+    if (cublasSetStream(h, (cudaStream_t)stream) != CUBLAS_STATUS_SUCCESS) return -14;
+    const float alpha = 1.f, beta = 0.f;
+    const cudaDataType_t t = dtype == CISR_BF16 ? CUDA_R_16BF : CUDA_R_32F;
+    const cudaDataType_t to = out_dtype == CISR_BF16 ? CUDA_R_16BF : CUDA_R_32F;
+    if (dtype == CISR_F32 && out_dtype != CISR_F32) return -2;
+    cublasStatus_t st = cublasGemmStridedBatchedEx(h, w_is_nk ? CUBLAS_OP_T : CUBLAS_OP_N, CUBLAS_OP_N, n, m, k, &alpha, w, t, ldw,
+                                                   stride_w, a, t, lda, stride_a, &beta, out, to, ldo, stride_o, batch,
+                                                   CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+    return st == CUBLAS_STATUS_SUCCESS ? 0 : -100 - (int)st;
+}

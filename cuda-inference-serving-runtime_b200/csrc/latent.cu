@@ -1,0 +1,161 @@
+// Latent attention: the small kernels around its matrix products.
+//
+// A token's keys and values are kept as one row of the cache: the normed latent c (kv_rank wide) followed by the
+// rotated key part that all heads share (rot_dim wide), padded with zeros to the cache's row width.  Queries are
+// brought to the same basis (q_h -> [W_uk_h^T q_h,plain | rotated part]) so attention runs over the rows as they are
+// stored, with the row's first kv_rank columns as the value; the value projection W_uv_h follows the weighted sum.
+//
+// Everything here is float arithmetic: unit norms, rotation (tables come in float from float64 angles), the gate's
+// sigmoid.  Storage is rounded once, on the way out.
+#include "common.cuh"
+
+static bool g_pdl = false;
+CISR_EXPORT void cisr_latent_set_pdl(int on) { g_pdl = on != 0; }
+
+// Rotated value of coordinate d (< 2 * rot_half) of a vector whose float coordinates are src[0 .. 2 * rot_half).
+__device__ __forceinline__ float rotated(const float* __restrict__ src, int d, int rot_half, int interleaved,
+                                         const float* __restrict__ cs, const float* __restrict__ sn) {
+    int f, other; bool first;
+    if (interleaved) { f = d >> 1; first = !(d & 1); other = first ? d + 1 : d - 1; }
+    else { first = d < rot_half; f = first ? d : d - rot_half; other = first ? d + rot_half : d - rot_half; }
+    const float c = cs[f], s = sn[f], v = src[d], o = src[other];
+    return first ? v * c - o * s : v * c + o * s;
+}
+
+// ---------------------------------------------------------------- down projections -> latents and cache row
+// proj [T, row_stride] float holds, per token, the query latent at q_col (q_rank wide; q_rank 0: none), the key/value
+// latent at c_col (kv_rank wide) and right behind it the shared key part (2 * rot_half wide).
+//   cq_out[t]            = unit(proj[q_col ..]) * q_norm_w                      (storage type of the next product)
+//   cache row of token t = [unit(proj[c_col ..]) * c_norm_w | rotate(key part) | 0 ...]
+// unit(v) = v / sqrt(mean(v^2) + eps).  The row lies in page block_table[slot][pos / P] at offset pos % P of a cache
+// laid out [pages, 1, P, row_width].
+template <typename CT>
+__global__ void latent_rows_kernel(const float* __restrict__ proj, int row_stride, int q_col, int q_rank,
+                                   const float* __restrict__ q_norm_w, CT* __restrict__ cq_out, int c_col, int kv_rank,
+                                   const float* __restrict__ c_norm_w, float eps, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t, int rot_half, int interleaved, CT* __restrict__ cache,
+                                   int row_width, const int* __restrict__ token_req, const int* __restrict__ positions,
+                                   const int* __restrict__ req_slot, const int* __restrict__ block_table, int table_width,
+                                   int page_size) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float* row = proj + (size_t)t * row_stride;
+    if (q_rank > 0) {
+        float sq = 0.f;
+        for (int d = threadIdx.x; d < q_rank; d += blockDim.x) { const float v = row[q_col + d]; sq += v * v; }
+        const float unit = rsqrtf(block_sum(sq, scratch) / (float)q_rank + eps);
+        for (int d = threadIdx.x; d < q_rank; d += blockDim.x)
+            cq_out[(size_t)t * q_rank + d] = from_float<CT>(row[q_col + d] * unit * q_norm_w[d]);
+    }
+    if (!cache) return;
+    float sq = 0.f;
+    for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) { const float v = row[c_col + d]; sq += v * v; }
+    const float unit = rsqrtf(block_sum(sq, scratch) / (float)kv_rank + eps);
+    const int pos = positions[t];
+    const int page = block_table[(size_t)req_slot[token_req[t]] * table_width + pos / page_size];
+    if (page < 0) return;      // the host reserves a page before every write; never follow a missing entry
+    CT* dst = cache + ((size_t)page * page_size + pos % page_size) * row_width;
+    const float* key = row + c_col + kv_rank;
+    const float* cs = cos_t + (size_t)t * rot_half;
+    const float* sn = sin_t + (size_t)t * rot_half;
+    for (int d = threadIdx.x; d < row_width; d += blockDim.x) {
+        float v = 0.f;
+        if (d < kv_rank) v = row[c_col + d] * unit * c_norm_w[d];
+        else if (d < kv_rank + 2 * rot_half) v = rotated(key, d - kv_rank, rot_half, interleaved, cs, sn);
+        dst[d] = from_float<CT>(v);
+    }
+}
+
+CISR_EXPORT int cisr_latent_rows(const float* proj, int row_stride, int q_col, int q_rank, const float* q_norm_w, void* cq_out,
+                                 int c_col, int kv_rank, const float* c_norm_w, float eps, const float* cos_t,
+                                 const float* sin_t, int rot_half, int interleaved, void* cache, int row_width, int dtype,
+                                 const int* token_req, const int* positions, const int* req_slot, const int* block_table,
+                                 int table_width, int page_size, int tokens, void* stream) {
+    if (tokens <= 0) return 0;
+    if (kv_rank + 2 * rot_half > row_width || rot_half < 0) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CISR_BF16)
+        return launch_kernel(latent_rows_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, s, g_pdl, proj, row_stride, q_col, q_rank,
+                             q_norm_w, (__nv_bfloat16*)cq_out, c_col, kv_rank, c_norm_w, eps, cos_t, sin_t, rot_half, interleaved,
+                             (__nv_bfloat16*)cache, row_width, token_req, positions, req_slot, block_table, table_width, page_size);
+    return launch_kernel(latent_rows_kernel<float>, dim3(tokens), dim3(128), 0, s, g_pdl, proj, row_stride, q_col, q_rank, q_norm_w,
+                         (float*)cq_out, c_col, kv_rank, c_norm_w, eps, cos_t, sin_t, rot_half, interleaved, (float*)cache, row_width,
+                         token_req, positions, req_slot, block_table, table_width, page_size);
+}
+
+// ---------------------------------------------------------------- queries: split and rotate
+// q [T, row_stride] float holds heads of [plain | rotated part] (plain_dim + 2 * rot_half wide) from column q_col on.
+//   plain_out[t, h, :]                          = the plain part (operand of the product with W_uk_h)
+//   q_rows[t, h, kv_rank .. kv_rank + rot)      = the rotated part, turned to the token's position
+//   q_rows[t, h, kv_rank + rot .. row_width)    = 0
+// q_rows[t, h, 0 .. kv_rank) is written by that product.
+template <typename CT>
+__global__ void latent_query_kernel(const float* __restrict__ q, int row_stride, int q_col, int heads, int plain_dim,
+                                    const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_half,
+                                    int interleaved, CT* __restrict__ plain_out, CT* __restrict__ q_rows, int kv_rank,
+                                    int row_width) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, rot = 2 * rot_half, head_w = plain_dim + rot;
+    const float* row = q + (size_t)t * row_stride + q_col;
+    const float* cs = cos_t + (size_t)t * rot_half;
+    const float* sn = sin_t + (size_t)t * rot_half;
+    for (int i = threadIdx.x; i < heads * plain_dim; i += blockDim.x) {
+        const int h = i / plain_dim, d = i - h * plain_dim;
+        plain_out[(size_t)t * heads * plain_dim + i] = from_float<CT>(row[h * head_w + d]);
+    }
+    const int tail = row_width - kv_rank;
+    for (int i = threadIdx.x; i < heads * tail; i += blockDim.x) {
+        const int h = i / tail, d = i - h * tail;
+        const float v = d < rot ? rotated(row + h * head_w + plain_dim, d, rot_half, interleaved, cs, sn) : 0.f;
+        q_rows[((size_t)t * heads + h) * row_width + kv_rank + d] = from_float<CT>(v);
+    }
+}
+
+CISR_EXPORT int cisr_latent_query(const float* q, int row_stride, int q_col, int heads, int plain_dim, const float* cos_t,
+                                  const float* sin_t, int rot_half, int interleaved, void* plain_out, void* q_rows,
+                                  int kv_rank, int row_width, int dtype, int tokens, void* stream) {
+    if (tokens <= 0) return 0;
+    if (kv_rank + 2 * rot_half > row_width) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CISR_BF16)
+        return launch_kernel(latent_query_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, s, g_pdl, q, row_stride, q_col, heads,
+                             plain_dim, cos_t, sin_t, rot_half, interleaved, (__nv_bfloat16*)plain_out, (__nv_bfloat16*)q_rows,
+                             kv_rank, row_width);
+    return launch_kernel(latent_query_kernel<float>, dim3(tokens), dim3(256), 0, s, g_pdl, q, row_stride, q_col, heads, plain_dim,
+                         cos_t, sin_t, rot_half, interleaved, (float*)plain_out, (float*)q_rows, kv_rank, row_width);
+}
+
+// ---------------------------------------------------------------- output gate
+// out[t, i] = values[t, i] * sigmoid(gate[t, gate_col + i]) (gate null: out = values), rounded to the storage type of
+// the output projection's operand.
+template <typename CT>
+__global__ void latent_gate_kernel(const float* __restrict__ values, const float* __restrict__ gate, int gate_stride,
+                                   int gate_col, CT* __restrict__ out, int width, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float v = values[i];
+    if (gate) {
+        const size_t t = i / width;
+        const float g = gate[t * gate_stride + gate_col + (i - t * width)];
+        v *= 1.f / (1.f + expf(-g));
+    }
+    out[i] = from_float<CT>(v);
+}
+
+CISR_EXPORT int cisr_latent_gate(const float* values, const float* gate, int gate_stride, int gate_col, void* out, int dtype,
+                                 int tokens, int width, void* stream) {
+    const size_t total = (size_t)tokens * width;
+    if (!total) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((unsigned)((total + 255) / 256));
+    if (dtype == CISR_BF16)
+        return launch_kernel(latent_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, g_pdl, values, gate, gate_stride, gate_col,
+                             (__nv_bfloat16*)out, width, total);
+    return launch_kernel(latent_gate_kernel<float>, grid, dim3(256), 0, s, g_pdl, values, gate, gate_stride, gate_col, (float*)out,
+                         width, total);
+}

@@ -1,0 +1,177 @@
+// Routed experts: a router that scores every expert per token, picks a few, and the chosen experts' small
+// feed-forward layers, summed with the router's weights.
+//
+//   scores s = sigmoid(W_router h)                       (float arithmetic whatever the storage type)
+//   experts form n_groups equal groups of neighbours; a group's score is the sum of its two best members; only members
+//   of the `keep` best groups can be chosen (n_groups 0: all can)
+//   the `top` best open experts are chosen, weight = s * route_scale (not renormalised)
+//   y = sum over chosen e of weight_e * W_down_e act(W_up_e h),   act(z) = max(z, 0)^2
+//
+// The expert products here: a warp per output feature, each chosen expert's rows streamed once per token that chose it
+// (moe_up_rows / moe_down_rows).
+#include "common.cuh"
+
+static bool g_pdl = false;
+CISR_EXPORT void cisr_moe_set_pdl(int on) { g_pdl = on != 0; }
+
+// Dot product of two rows of n values, the warp's lanes striding over them; 16-byte loads where the rows allow.
+__device__ __forceinline__ float warp_dot(const float* __restrict__ a, const float* __restrict__ b, int n, int lane) {
+    float acc = 0.f;
+    if (!(n & 3) && !(((uintptr_t)a | (uintptr_t)b) & 15)) {
+        const float4* a4 = reinterpret_cast<const float4*>(a);
+        const float4* b4 = reinterpret_cast<const float4*>(b);
+        for (int i = lane; i < (n >> 2); i += 32) {
+            const float4 x = a4[i], y = b4[i];
+            acc += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) acc += a[i] * b[i];
+    }
+    return warp_sum(acc);
+}
+__device__ __forceinline__ float warp_dot(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b, int n, int lane) {
+    float acc = 0.f;
+    if (!(n & 7) && !(((uintptr_t)a | (uintptr_t)b) & 15)) {
+        const uint4* a4 = reinterpret_cast<const uint4*>(a);
+        const uint4* b4 = reinterpret_cast<const uint4*>(b);
+        for (int i = lane; i < (n >> 3); i += 32) {
+            const uint4 x = a4[i], y = b4[i];
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
+            const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 xf = __bfloat1622float2(xp[j]), yf = __bfloat1622float2(yp[j]);
+                acc += xf.x * yf.x + xf.y * yf.y;
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) acc += __bfloat162float(a[i]) * __bfloat162float(b[i]);
+    }
+    return warp_sum(acc);
+}
+
+// ---------------------------------------------------------------- router
+// One CTA per token.  Shared memory: n_experts scores, n_experts flags, n_groups group scores.
+template <typename T>
+__global__ void moe_router_kernel(const T* __restrict__ h, const T* __restrict__ w, int hidden, int n_experts, int top,
+                                  int n_groups, int keep, float route_scale, int* __restrict__ chosen,
+                                  float* __restrict__ weight) {
+    extern __shared__ float smem[];
+    float* score = smem;
+    int* open_ = reinterpret_cast<int*>(smem + n_experts);
+    float* group_score = smem + 2 * n_experts;
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const T* row = h + (size_t)t * hidden;
+    for (int e = warp; e < n_experts; e += n_warps) {
+        const float z = warp_dot(w + (size_t)e * hidden, row, hidden, lane);
+        if (lane == 0) score[e] = 1.f / (1.f + expf(-z));
+    }
+    __syncthreads();
+    if (n_groups > 0) {
+        const int per = n_experts / n_groups;
+        for (int g = threadIdx.x; g < n_groups; g += blockDim.x) {
+            float best = -1.f, second = -1.f;
+            for (int i = 0; i < per; ++i) {
+                const float s = score[g * per + i];
+                if (s > best) { second = best; best = s; }
+                else if (s > second) second = s;
+            }
+            group_score[g] = per > 1 ? best + second : best;
+        }
+    }
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) open_[e] = n_groups > 0 ? 0 : 1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (n_groups > 0) {
+            const int per = n_experts / n_groups;
+            for (int k = 0; k < keep; ++k) {          // the best groups, one after the other; ties go to the lower index
+                int best = -1;
+                for (int g = 0; g < n_groups; ++g)
+                    if (group_score[g] >= 0.f && (best < 0 || group_score[g] > group_score[best])) best = g;
+                if (best < 0) break;
+                group_score[best] = -1.f;
+                for (int i = 0; i < per; ++i) open_[best * per + i] = 1;
+            }
+        }
+        for (int k = 0; k < top; ++k) {
+            int best = -1;
+            for (int e = 0; e < n_experts; ++e)
+                if (open_[e] && (best < 0 || score[e] > score[best])) best = e;
+            if (best < 0) best = 0;                    // fewer open experts than `top`: the host refuses such a configuration
+            else open_[best] = 0;
+            chosen[(size_t)t * top + k] = best;
+            weight[(size_t)t * top + k] = score[best] * route_scale;
+        }
+    }
+}
+
+CISR_EXPORT int cisr_moe_router(const void* h, const void* w, int dtype, int tokens, int hidden, int n_experts, int top,
+                                int n_groups, int keep, float route_scale, int* chosen, float* weight, void* stream) {
+    if (tokens <= 0) return 0;
+    if (n_experts <= 0 || top <= 0 || top > n_experts || (n_groups > 0 && (n_experts % n_groups || keep <= 0 || keep > n_groups)))
+        return -2;
+    const size_t smem = (size_t)(2 * n_experts + (n_groups > 0 ? n_groups : 0)) * sizeof(float);
+    if (smem > 48 * 1024) return -3;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CISR_BF16)
+        return launch_kernel(moe_router_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), smem, s, g_pdl, (const __nv_bfloat16*)h,
+                             (const __nv_bfloat16*)w, hidden, n_experts, top, n_groups, keep, route_scale, chosen, weight);
+    return launch_kernel(moe_router_kernel<float>, dim3(tokens), dim3(128), smem, s, g_pdl, (const float*)h, (const float*)w, hidden,
+                         n_experts, top, n_groups, keep, route_scale, chosen, weight);
+}
+
+// ---------------------------------------------------------------- few tokens: a warp per output feature
+// act[t * top + k, f] = max(W_up[e][f] . h[t], 0)^2 with e = chosen[t, k];   W_up [experts, ff, hidden].
+constexpr int ROW_WARPS = 8;
+template <typename T>
+__global__ void __launch_bounds__(32 * ROW_WARPS)
+moe_up_rows_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __restrict__ chosen, int hidden, int ff,
+                   int top, T* __restrict__ act) {
+    pdl_trigger();
+    pdl_wait();
+    const int pair = blockIdx.x, lane = threadIdx.x & 31, f = blockIdx.y * ROW_WARPS + (threadIdx.x >> 5);
+    if (f >= ff) return;
+    const int e = chosen[pair];
+    const float z = warp_dot(w_up + ((size_t)e * ff + f) * hidden, h + (size_t)(pair / top) * hidden, hidden, lane);
+    if (lane == 0) { const float r = fmaxf(z, 0.f); act[(size_t)pair * ff + f] = from_float<T>(r * r); }
+}
+
+// out[t, c] = sum_k weight[t, k] * (W_down[e_k][c] . act[t * top + k]);   W_down [experts, hidden, ff]; experts in the
+// order the router chose them.
+template <typename T>
+__global__ void __launch_bounds__(32 * ROW_WARPS)
+moe_down_rows_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ chosen,
+                     const float* __restrict__ weight, int hidden, int ff, int top, float* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, c = blockIdx.y * ROW_WARPS + (threadIdx.x >> 5);
+    if (c >= hidden) return;
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) {
+        const int e = chosen[(size_t)t * top + k];
+        acc += weight[(size_t)t * top + k] * warp_dot(w_down + ((size_t)e * hidden + c) * ff, act + ((size_t)t * top + k) * ff, ff, lane);
+    }
+    if (lane == 0) out[(size_t)t * hidden + c] = acc;
+}
+
+CISR_EXPORT int cisr_moe_rows(const void* h, const void* w_up, const void* w_down, int dtype, const int* chosen,
+                              const float* weight, int tokens, int hidden, int ff, int top, void* act, float* out, void* stream) {
+    if (tokens <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 up_grid(tokens * top, (ff + ROW_WARPS - 1) / ROW_WARPS), down_grid(tokens, (hidden + ROW_WARPS - 1) / ROW_WARPS);
+    int st;
+    if (dtype == CISR_BF16) {
+        st = launch_kernel(moe_up_rows_kernel<__nv_bfloat16>, up_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl, (const __nv_bfloat16*)h,
+                           (const __nv_bfloat16*)w_up, chosen, hidden, ff, top, (__nv_bfloat16*)act);
+        if (st) return st;
+        return launch_kernel(moe_down_rows_kernel<__nv_bfloat16>, down_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl,
+                             (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, chosen, weight, hidden, ff, top, out);
+    }
+    st = launch_kernel(moe_up_rows_kernel<float>, up_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl, (const float*)h, (const float*)w_up,
+                       chosen, hidden, ff, top, (float*)act);
+    if (st) return st;
+    return launch_kernel(moe_down_rows_kernel<float>, down_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl, (const float*)act,
+                         (const float*)w_down, chosen, weight, hidden, ff, top, out);
+}

@@ -49,6 +49,7 @@ class Model:
             self.layers.append(ARRANGEMENTS[layer_spec.arrangement](layer_spec, self.dtype))
         self.final_norm = build_part(NORMS, spec.final_norm, self.dtype, "norm")
         self.head = build_part(HEADS, spec.head, self.dtype, "head")
+        self.pass_steps = None if spec.pass_steps is None else build_part(EMBEDDINGS, spec.pass_steps, self.dtype, "per-pass vectors")
         self.loaded = False
 
     # ---------------------------------------------------------------- tensors
@@ -57,6 +58,8 @@ class Model:
         for layer_spec, layer in zip(self.spec.layers, self.layers):
             for slot, part in layer.parts().items():
                 yield layer_spec.prefix + layer_spec.names.get(slot, slot + "."), part
+        if self.pass_steps is not None:
+            yield self.spec.pass_steps_prefix, self.pass_steps
         yield self.spec.final_norm_prefix, self.final_norm
         yield self.spec.head_prefix, self.head
 
@@ -134,10 +137,14 @@ class Model:
             part.begin_step(ctx)
         stream = ResidualStream(self.embedding.forward(ctx.token_ids))
         for index, entry in enumerate(self.spec.run):
+            if entry.pass_step is not None:
+                self.pass_steps.add_to(stream, entry.pass_step)
             self.layers[entry.layer].forward(stream, ctx, cache.binding(index, reads_from=entry.cache_of))
         if ctx.logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
-        h = self.final_norm.forward(stream.x, stream.take_pending(), self.dtype, rows=ctx.logit_rows, write_back=False)
+        scale = stream.pending_scale
+        extra = {} if scale is None else {"delta_scale": scale}
+        h = self.final_norm.forward(stream.x, stream.take_pending(), self.dtype, rows=ctx.logit_rows, write_back=False, **extra)
         return self.head.forward(h)
 
     # ---------------------------------------------------------------- construction

@@ -46,7 +46,7 @@ def run_page_copies(cache: CacheManager, device) -> None:
         if copies:
             pairs = torch.tensor(copies, dtype=torch.int32, device=device)
             page_bytes = g.page_bytes()
-            kernels.page_copy(g.storage, pairs, g.storage.shape[0] * 2, g.pool.n_pages * page_bytes, page_bytes)
+            kernels.page_copy(g.storage, pairs, g.storage.shape[0] * g.storage.shape[1], g.pool.n_pages * page_bytes, page_bytes)
 
 
 def prepare_step(cache: CacheManager, ring: PinnedRing, device, entries: Sequence[StepEntry], vocab_size: int,

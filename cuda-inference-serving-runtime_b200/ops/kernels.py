@@ -80,24 +80,28 @@ def _elementwise():
         lib.cisr_rope_store.restype = ctypes.c_int
         lib.cisr_page_copy.restype = ctypes.c_int
         lib.cisr_table_update.restype = ctypes.c_int
+        lib.cisr_stream_add.restype = ctypes.c_int
+        lib.cisr_scale.restype = ctypes.c_int
         lib._typed = True
     return lib
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, :] = table[ids[t], :] widened to float."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[t, :] = table[ids[t], :] widened to float, times `scale`."""
     _need(table, None, "table", 2); _need(ids, torch.int32, "ids", 1); _need(out, torch.float32, "out", 2)
     tokens, hidden = out.shape
     if ids.numel() != tokens or table.shape[1] != hidden:
         raise KernelError("embedding: shapes of ids, table and out disagree")
     _check(_elementwise().cisr_embedding(_p(table), dtype_code(table.dtype), _p(ids), _p(out), tokens, hidden,
-                                         table.shape[0], _stream()), "embedding")
+                                         table.shape[0], ctypes.c_float(scale), _stream()), "embedding")
     return out
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
-                rows: Optional[torch.Tensor] = None, write_back: bool = True) -> torch.Tensor:
-    """x += delta (when given), out = rmsnorm(x) * weight; `rows` selects which rows of x become rows of out."""
+                rows: Optional[torch.Tensor] = None, write_back: bool = True,
+                delta_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x += delta (when given; times the per-channel `delta_scale` when that is given), out = rmsnorm(x) * weight;
+    `rows` selects which rows of x become rows of out."""
     _need(x, torch.float32, "x", 2); _need(weight, None, "weight", 1); _need(out, None, "out", 2)
     hidden = x.shape[1]
     if delta is not None:
@@ -113,10 +117,41 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
         raise KernelError("add_rmsnorm: out and x differ in rows")
     if weight.numel() != hidden or out.shape[1] != hidden:
         raise KernelError("add_rmsnorm: width mismatch")
+    if delta_scale is not None:
+        _need(delta_scale, torch.float32, "delta_scale", 1)
+        if delta_scale.numel() != hidden:
+            raise KernelError("add_rmsnorm: one scale per channel is needed")
     _check(_elementwise().cisr_add_rmsnorm(_p(x), _p(delta), _p(weight), dtype_code(weight.dtype), _p(out),
                                            dtype_code(out.dtype), _p(rows), n_rows, hidden, ctypes.c_float(eps),
-                                           int(write_back), _stream()), "add_rmsnorm")
+                                           int(write_back), _p(delta_scale if delta is not None else None), _stream()),
+           "add_rmsnorm")
     return out
+
+
+def stream_add(x: torch.Tensor, delta: Optional[torch.Tensor] = None, delta_scale: Optional[torch.Tensor] = None,
+               vector: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[t, :] += delta[t, :] * delta_scale + vector, in place; each of the three may be absent."""
+    _need(x, torch.float32, "x", 2)
+    tokens, hidden = x.shape
+    if delta is not None:
+        _need(delta, torch.float32, "delta", 2)
+        if delta.shape != x.shape:
+            raise KernelError("stream_add: delta and x differ in shape")
+    for name, t in (("delta_scale", delta_scale), ("vector", vector)):
+        if t is not None:
+            _need(t, torch.float32, name, 1)
+            if t.numel() != hidden:
+                raise KernelError(f"stream_add: {name} must have one value per channel")
+    _check(_elementwise().cisr_stream_add(_p(x), _p(delta), _p(delta_scale if delta is not None else None), _p(vector), tokens,
+                                          hidden, _stream()), "stream_add")
+    return x
+
+
+def scale_(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """x *= scale, in place (float)."""
+    _need(x, torch.float32, "x")
+    _check(_elementwise().cisr_scale(_p(x), ctypes.c_longlong(x.numel()), ctypes.c_float(scale), _stream()), "scale")
+    return x
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -407,6 +442,139 @@ def merge_out_proj(partial: torch.Tensor, stats: torch.Tensor, n_splits: int, de
     return out
 
 
+# ------------------------------------------------------------------ latent attention: the kernels around its products
+_latent_state = {}
+
+
+def _latent():
+    lib = _latent_state.get("lib")
+    if lib is None:
+        lib = load_library("latent.cu")
+        for name in ("cisr_latent_rows", "cisr_latent_query", "cisr_latent_gate"):
+            getattr(lib, name).restype = ctypes.c_int
+        lib.cisr_latent_set_pdl(int(_pdl_state["on"]))
+        _latent_state["lib"] = lib
+    return lib
+
+
+def latent_jobs():
+    return [("latent.cu", {}, ())]
+
+
+def latent_rows(proj: torch.Tensor, q_col: int, q_rank: int, q_norm_w: Optional[torch.Tensor], cq_out: Optional[torch.Tensor],
+                c_col: int, kv_rank: int, c_norm_w: torch.Tensor, eps: float, cos: torch.Tensor, sin: torch.Tensor,
+                rot_half: int, interleaved: bool, cache: Optional[torch.Tensor], token_req, positions, req_slot, block_table,
+                page_size: int) -> None:
+    """From the stacked down projections `proj` (float [tokens, columns]): the unit-normed query latent (`q_rank` columns
+    from `q_col`, to `cq_out`; q_rank 0: none) and the token's cache row [unit-normed latent | rotated shared key part | 0]
+    written into its page of `cache` [pages, 1, page_size, row width] (None: the row is not written)."""
+    _need(proj, torch.float32, "proj", 2); _need(c_norm_w, torch.float32, "c_norm_w", 1)
+    _need(cos, torch.float32, "cos", 2); _need(sin, torch.float32, "sin", 2)
+    tokens = proj.shape[0]
+    if cos.shape != (tokens, rot_half) or sin.shape != cos.shape:
+        raise KernelError("latent_rows: rotary tables must be [tokens, rot_half]")
+    dtype = None
+    if q_rank:
+        _need(q_norm_w, torch.float32, "q_norm_w", 1); _need(cq_out, None, "cq_out", 2)
+        if cq_out.shape != (tokens, q_rank) or q_norm_w.numel() != q_rank or q_col + q_rank > proj.shape[1]:
+            raise KernelError("latent_rows: query latent shapes disagree")
+        dtype = cq_out.dtype
+    row_width = 0
+    if cache is not None:
+        _need(cache, dtype, "cache", 4)
+        if cache.shape[1] != 1 or cache.shape[2] != page_size:
+            raise KernelError("latent_rows: cache must be [pages, 1, page_size, row width]")
+        row_width = cache.shape[3]
+        dtype = cache.dtype
+        if c_col + kv_rank + 2 * rot_half > proj.shape[1] or c_norm_w.numel() != kv_rank:
+            raise KernelError("latent_rows: key/value latent shapes disagree")
+    for name, t in (("token_req", token_req), ("positions", positions), ("req_slot", req_slot), ("block_table", block_table)):
+        _need(t, torch.int32, name)
+    _check(_latent().cisr_latent_rows(
+        _p(proj), proj.shape[1], q_col, q_rank, _p(q_norm_w), _p(cq_out), c_col, kv_rank, _p(c_norm_w), ctypes.c_float(eps),
+        _p(cos), _p(sin), rot_half, int(interleaved), _p(cache), row_width, dtype_code(dtype), _p(token_req), _p(positions),
+        _p(req_slot), _p(block_table), block_table.shape[1], page_size, tokens, _stream()), "latent_rows")
+
+
+def latent_query(q: torch.Tensor, q_col: int, heads: int, plain_dim: int, cos: torch.Tensor, sin: torch.Tensor, rot_half: int,
+                 interleaved: bool, plain_out: torch.Tensor, q_rows: torch.Tensor, kv_rank: int) -> None:
+    """Split the heads of `q` (float [tokens, columns], heads of [plain | rotated part] from `q_col` on): the plain parts
+    go to `plain_out` [tokens, heads, plain_dim]; the rotated parts, turned to the tokens' positions, go to columns
+    kv_rank .. of `q_rows` [tokens, heads, row width], the columns behind them are zeroed."""
+    _need(q, torch.float32, "q", 2); _need(plain_out, q_rows.dtype, "plain_out", 3); _need(q_rows, None, "q_rows", 3)
+    _need(cos, torch.float32, "cos", 2); _need(sin, torch.float32, "sin", 2)
+    tokens = q.shape[0]
+    if (plain_out.shape != (tokens, heads, plain_dim) or q_rows.shape[:2] != (tokens, heads)
+            or q_col + heads * (plain_dim + 2 * rot_half) > q.shape[1] or cos.shape != (tokens, rot_half)):
+        raise KernelError("latent_query: shapes disagree")
+    _check(_latent().cisr_latent_query(_p(q), q.shape[1], q_col, heads, plain_dim, _p(cos), _p(sin), rot_half, int(interleaved),
+                                       _p(plain_out), _p(q_rows), kv_rank, q_rows.shape[2], dtype_code(q_rows.dtype), tokens,
+                                       _stream()), "latent_query")
+
+
+def latent_gate(values: torch.Tensor, gate: Optional[torch.Tensor], gate_col: int, out: torch.Tensor) -> torch.Tensor:
+    """out = values * sigmoid(gate[:, gate_col : gate_col + width]) (gate None: out = values), rounded to out's type."""
+    _need(values, torch.float32, "values", 2); _need(out, None, "out", 2)
+    tokens, width = values.shape
+    if out.shape != values.shape:
+        raise KernelError("latent_gate: out and values differ in shape")
+    if gate is not None:
+        _need(gate, torch.float32, "gate", 2)
+        if gate.shape[0] != tokens or gate_col + width > gate.shape[1]:
+            raise KernelError("latent_gate: the gate's columns lie outside its rows")
+    _check(_latent().cisr_latent_gate(_p(values), _p(gate), gate.shape[1] if gate is not None else 0, gate_col, _p(out),
+                                      dtype_code(out.dtype), tokens, width, _stream()), "latent_gate")
+    return out
+
+
+# ------------------------------------------------------------------ routed experts
+_moe_state = {}
+
+
+def _moe():
+    lib = _moe_state.get("lib")
+    if lib is None:
+        lib = load_library("moe.cu")
+        for name in ("cisr_moe_router", "cisr_moe_rows"):
+            getattr(lib, name).restype = ctypes.c_int
+        lib.cisr_moe_set_pdl(int(_pdl_state["on"]))
+        _moe_state["lib"] = lib
+    return lib
+
+
+def moe_jobs():
+    return [("moe.cu", {}, ())]
+
+
+def moe_router(h: torch.Tensor, w: torch.Tensor, top: int, n_groups: int, keep: int, route_scale: float,
+               chosen: torch.Tensor, weight: torch.Tensor) -> None:
+    """Per token: sigmoid scores of every expert (float arithmetic), the open groups, the `top` chosen experts
+    (`chosen`, int32 [tokens, top], best first) and their weights score * route_scale (`weight`, float)."""
+    _need(h, None, "h", 2); _need(w, h.dtype, "w", 2); _need(chosen, torch.int32, "chosen", 2); _need(weight, torch.float32, "weight", 2)
+    tokens, hidden = h.shape
+    if w.shape[1] != hidden or chosen.shape != (tokens, top) or weight.shape != (tokens, top):
+        raise KernelError("moe_router: shapes disagree")
+    _check(_moe().cisr_moe_router(_p(h), _p(w), dtype_code(h.dtype), tokens, hidden, w.shape[0], top, n_groups, keep,
+                                  ctypes.c_float(route_scale), _p(chosen), _p(weight), _stream()), "moe_router")
+
+
+def moe_rows(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
+             act: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out (float [tokens, hidden]) = sum over a token's chosen experts of weight * W_down_e relu(W_up_e h)^2, a warp per
+    output feature; w_up [experts, ff, hidden], w_down [experts, hidden, ff]; `act` [tokens * top, ff] is scratch."""
+    _need(h, None, "h", 2); _need(w_up, h.dtype, "w_up", 3); _need(w_down, h.dtype, "w_down", 3); _need(act, h.dtype, "act", 2)
+    _need(out, torch.float32, "out", 2); _need(chosen, torch.int32, "chosen", 2); _need(weight, torch.float32, "weight", 2)
+    tokens, hidden = h.shape
+    experts, ff, _ = w_up.shape
+    top = chosen.shape[1]
+    if (w_up.shape[2] != hidden or w_down.shape != (experts, hidden, ff) or act.shape != (tokens * top, ff)
+            or out.shape != (tokens, hidden) or chosen.shape[0] != tokens or weight.shape != chosen.shape):
+        raise KernelError("moe_rows: shapes disagree")
+    _check(_moe().cisr_moe_rows(_p(h), _p(w_up), _p(w_down), dtype_code(h.dtype), _p(chosen), _p(weight), tokens, hidden, ff, top,
+                                _p(act), _p(out), _stream()), "moe_rows", own=2)
+    return out
+
+
 # ------------------------------------------------------------------ sampling
 def _sampling():
     lib = load_library("sampling.cu")
@@ -467,6 +635,7 @@ def _gemm_library():
         lib = load_library("gemm_library.cu", extra=("-lcublas",))
         lib.cisr_gemm_library_init.restype = ctypes.c_int
         lib.cisr_gemm_library.restype = ctypes.c_int
+        lib.cisr_gemm_library_batched.restype = ctypes.c_int
         workspace = torch.empty(GEMM_WORKSPACE_BYTES, dtype=torch.uint8, device="cuda")
         _check(lib.cisr_gemm_library_init(_p(workspace), ctypes.c_longlong(GEMM_WORKSPACE_BYTES)), "gemm library init")
         _gemm_state["lib"], _gemm_state["workspace"] = lib, workspace
@@ -482,6 +651,28 @@ def gemm_library(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.T
         raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
     _check(_gemm_library().cisr_gemm_library(_p(a), _p(w), dtype_code(a.dtype), _p(out), m, n, k, _stream()), "gemm",
            own=0, library=1)
+    return out
+
+
+def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, w_is_nk: bool) -> torch.Tensor:
+    """One product per head by the vendor library: out[:, h, :n] = a[:, h, :k] @ w_h, float accumulation.
+
+    a [M, H, >= k] and out [M, H, >= n] may be wider than the product uses (their last axis is the row of a head, of
+    which the first k or n columns take part); w [H, n, k] (`w_is_nk`, the checkpoint's [out, in] layout per head) or
+    [H, k, n].  out is float or has the operands' type."""
+    _need(w, a.dtype, "w", 3); _need(a, None, "a", 3); _need(out, None, "out", 3)
+    heads = w.shape[0]
+    n, k = (w.shape[1], w.shape[2]) if w_is_nk else (w.shape[2], w.shape[1])
+    m = a.shape[0]
+    if a.shape[1] != heads or out.shape[1] != heads or out.shape[0] != m or a.shape[2] < k or out.shape[2] < n:
+        raise KernelError(f"gemm_heads: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
+    if out.dtype not in (torch.float32, a.dtype):
+        raise KernelError("gemm_heads: out must be float or of the operands' type")
+    lib = _gemm_library()
+    _check(lib.cisr_gemm_library_batched(
+        _p(a), heads * a.shape[2], ctypes.c_longlong(a.shape[2]), _p(w), w.shape[2], ctypes.c_longlong(w.shape[1] * w.shape[2]),
+        int(w_is_nk), dtype_code(a.dtype), _p(out), heads * out.shape[2], ctypes.c_longlong(out.shape[2]), dtype_code(out.dtype),
+        m, n, k, heads, _stream()), "gemm_heads", own=0, library=1)
     return out
 
 
@@ -529,6 +720,10 @@ def set_pdl(on: bool) -> None:
         _merge_proj_state["lib"].cisr_merge_proj_set_pdl(int(on))
     _elementwise().cisr_elementwise_set_pdl(int(on))
     _sampling().cisr_sampling_set_pdl(int(on))
+    if "lib" in _latent_state:
+        _latent_state["lib"].cisr_latent_set_pdl(int(on))
+    if "lib" in _moe_state:
+        _moe_state["lib"].cisr_moe_set_pdl(int(on))
     if "lib" in _tcgen05_state:
         _tcgen05_state["lib"].cisr_gemm_tcgen05_set_pdl(int(on))
     for (source, _, _), lib in list(_attention_libs.items()):
@@ -797,8 +992,16 @@ def _describe_gemm(a, w, *rest, **kw):
 
 
 _DESCRIBE = {
-    "embedding": lambda table, ids, out: (int(out.shape[0]), int(out.shape[1])),
-    "add_rmsnorm": lambda x, delta, weight, eps, out, rows=None, write_back=True: (int(out.shape[0]), int(out.shape[1]), delta is not None),
+    "embedding": lambda table, ids, out, scale=1.0: (int(out.shape[0]), int(out.shape[1])),
+    "add_rmsnorm": lambda x, delta, weight, eps, out, rows=None, write_back=True, delta_scale=None: (int(out.shape[0]), int(out.shape[1]), delta is not None),
+    "stream_add": lambda x, *a, **kw: (int(x.shape[0]), int(x.shape[1])),
+    "scale_": lambda x, scale: (int(x.numel()),),
+    "latent_rows": lambda proj, *a, **kw: (int(proj.shape[0]), int(proj.shape[1])),
+    "latent_query": lambda q, *a, **kw: (int(q.shape[0]), int(q.shape[1])),
+    "latent_gate": lambda values, *a, **kw: (int(values.shape[0]), int(values.shape[1])),
+    "moe_router": lambda h, w, *a, **kw: (int(h.shape[0]), int(w.shape[0]), int(w.shape[1])),
+    "moe_rows": lambda h, w_up, *a, **kw: (int(h.shape[0]), int(w_up.shape[0]), int(w_up.shape[1]), int(w_up.shape[2])),
+    "gemm_heads": lambda a, w, out, w_is_nk: (int(a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2])),
     "swiglu": lambda gate_up, out: (int(out.shape[0]), int(out.shape[1])),
     "rotary_tables": lambda positions, inv_freq, cos, sin: (int(cos.shape[0]), int(cos.shape[1])),
     "rope_store": lambda proj, *rest, **kw: (int(proj.shape[0]), int(proj.shape[1])),

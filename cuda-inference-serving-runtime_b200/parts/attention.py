@@ -71,36 +71,10 @@ class GQAAttention(Mixer):
 
     # ---------------------------------------------------------------- the launch plan of a step
     def plan_key(self):
-        return ("gqa_attention", kernels.PREFILL_TILE, kernels.WIDE_TILE, DECODE_RANGE)
+        return ATTENTION_PLAN_KEY
 
     def step_plan(self, host):
-        """Which CTAs the attention kernels launch for a step: portions of more than one token are cut into query
-        tiles (request, first query), once per tile size of the two prompt kernels, a portion's last tile first (it
-        has the longest key loop); single tokens are listed for the split kernel, whose number of key ranges comes
-        from the longest context among them (or from the bound a captured graph was made for)."""
-        from ..engine.batch import StepPlan
-
-        tile_req, tile_q0, wide_req, wide_q0, dec_req = [], [], [], [], []
-        longest = 0
-        for r, n in enumerate(host.q_len):
-            if n == 1:
-                dec_req.append(r)
-                longest = max(longest, host.ctx_len[r])
-            else:
-                for q0 in reversed(range(0, n, kernels.PREFILL_TILE)):
-                    tile_req.append(r)
-                    tile_q0.append(q0)
-                for q0 in reversed(range(0, n, kernels.WIDE_TILE)):
-                    wide_req.append(r)
-                    wide_q0.append(q0)
-        if dec_req and host.ctx_bound:
-            longest = max(longest, host.ctx_bound)
-        as_i32 = lambda values: np.asarray(values, dtype=np.int32)
-        return StepPlan(
-            arrays={"tile_req": as_i32(tile_req), "tile_q0": as_i32(tile_q0), "wide_req": as_i32(wide_req),
-                    "wide_q0": as_i32(wide_q0), "dec_req": as_i32(dec_req)},
-            info={"n_tiles": len(tile_req), "n_wide": len(wide_req), "n_decode": len(dec_req),
-                  "n_splits": decode_ranges(longest)})
+        return attention_step_plan(host)
 
     def begin_step(self, ctx) -> None:
         self.position.rotation(ctx)          # the rotation tables of the step, shared by every layer with the same encoding
@@ -183,3 +157,60 @@ def decode_ranges(longest_context: int) -> int:
     if n > CLUSTER_MAX:
         n = -(-n // CLUSTER_MAX) * CLUSTER_MAX
     return n
+
+
+ATTENTION_PLAN_KEY = ("paged_attention", kernels.PREFILL_TILE, kernels.WIDE_TILE, DECODE_RANGE)
+
+
+def attention_step_plan(host):
+    """Which CTAs the attention kernels launch for a step: portions of more than one token are cut into query
+    tiles (request, first query), once per tile size of the two prompt kernels, a portion's last tile first (it
+    has the longest key loop); single tokens are listed for the split kernel, whose number of key ranges comes
+    from the longest context among them (or from the bound a captured graph was made for).  Every mixer that runs
+    the paged attention kernels shares this plan (`ATTENTION_PLAN_KEY`)."""
+    from ..engine.batch import StepPlan
+
+    tile_req, tile_q0, wide_req, wide_q0, dec_req = [], [], [], [], []
+    longest = 0
+    for r, n in enumerate(host.q_len):
+        if n == 1:
+            dec_req.append(r)
+            longest = max(longest, host.ctx_len[r])
+        else:
+            for q0 in reversed(range(0, n, kernels.PREFILL_TILE)):
+                tile_req.append(r)
+                tile_q0.append(q0)
+            for q0 in reversed(range(0, n, kernels.WIDE_TILE)):
+                wide_req.append(r)
+                wide_q0.append(q0)
+    if dec_req and host.ctx_bound:
+        longest = max(longest, host.ctx_bound)
+    as_i32 = lambda values: np.asarray(values, dtype=np.int32)
+    return StepPlan(
+        arrays={"tile_req": as_i32(tile_req), "tile_q0": as_i32(tile_q0), "wide_req": as_i32(wide_req),
+                "wide_q0": as_i32(wide_q0), "dec_req": as_i32(dec_req)},
+        info={"n_tiles": len(tile_req), "n_wide": len(wide_req), "n_decode": len(dec_req),
+              "n_splits": decode_ranges(longest)})
+
+
+def paged_attention(plan, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cache, ctx, hq: int, hkv: int, scale: float,
+                    window) -> torch.Tensor:
+    """Attention of a step's queries q [tokens, hq, D] over the pages of k and v ([pages, hkv, page, D]; the same tensor
+    where a row serves as key and value), with the step's launch plan: the prompt kernel for portions, the split kernel
+    and its merge for single tokens.  Returns [tokens, hq, D] in q's type."""
+    tokens, _, dim = q.shape
+    out = torch.empty_like(q)
+    if plan.info["n_tiles"] and kernels.attn_prefill_wide_ok(q, k, cache.page_size):
+        kernels.attn_prefill_wide(q, out, k, v, ctx.req_slot, cache.block_table, plan["wide_req"], plan["wide_q0"],
+                                  ctx.q_start, ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, scale, window)
+    elif plan.info["n_tiles"]:
+        kernels.attn_prefill(q, out, k, v, ctx.req_slot, cache.block_table, plan["tile_req"], plan["tile_q0"],
+                             ctx.q_start, ctx.q_len, ctx.ctx_len, hq, hkv, cache.page_size, scale, window)
+    n_decode = plan.info["n_decode"]
+    if n_decode:
+        n_splits = plan.info["n_splits"]
+        partial = torch.empty((n_decode, hq, n_splits, dim), dtype=torch.float32, device=q.device)
+        stats = torch.empty((n_decode, hq, n_splits, 2), dtype=torch.float32, device=q.device)
+        kernels.attn_decode(q, out, k, v, ctx.req_slot, cache.block_table, plan["dec_req"], n_decode, ctx.q_start,
+                            ctx.ctx_len, partial, stats, hq, hkv, cache.page_size, scale, window, DECODE_RANGE, n_splits)
+    return out

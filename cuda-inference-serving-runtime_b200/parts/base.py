@@ -27,10 +27,13 @@ class TensorNeed:
     role "vector": a small per-channel tensor, kept as stored when stored in 32-bit, else in the compute dtype.
     role "table": an integer table, kept as int32.
     `alias` names a tensor (by full checkpoint name) to use when this one is absent (a tied head).
+    `init_std` is the spread seeded random weights are drawn with when the default does not suit the tensor (a router
+    whose scores must not all be alike).
     """
     shape: Tuple[int, ...]
     role: str = "matrix"
     alias: Optional[str] = None
+    init_std: Optional[float] = None
 
 
 class Part:
@@ -77,10 +80,12 @@ class PendingNorm:
         self.stream, self.norm, self.dtype = stream, norm, dtype
         self.x = stream.x
         self.delta = stream.pending
+        self.delta_scale = getattr(stream, "pending_scale", None)
         self.resolved = False      # the norm has run (here or inside a product): stream.x is the sum, nothing is pending
 
     def fusable(self) -> bool:
-        return getattr(self.norm, "fusable_into_product", False)
+        # a pending output that still has to be scaled per channel is added by the norm's own kernel
+        return getattr(self.norm, "fusable_into_product", False) and (self.delta is None or self.delta_scale is None)
 
     @property
     def weight(self) -> torch.Tensor:
@@ -101,7 +106,12 @@ class PendingNorm:
         self.resolved = True
 
     def materialize(self) -> torch.Tensor:
-        out = self.norm.forward(self.stream.x, self.stream.take_pending(), self.dtype)
+        scale = getattr(self.stream, "pending_scale", None)
+        delta = self.stream.take_pending()
+        if scale is not None and delta is not None:
+            out = self.norm.forward(self.stream.x, delta, self.dtype, delta_scale=scale)
+        else:
+            out = self.norm.forward(self.stream.x, delta, self.dtype)
         self.resolved = True
         return out
 
@@ -114,8 +124,10 @@ class PendingNorm:
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
-                rows: Optional[torch.Tensor] = None, write_back: bool = True) -> torch.Tensor:
-        """x += delta in place (if given), then return norm(x) in `out_dtype`; `rows` picks rows of x."""
+                rows: Optional[torch.Tensor] = None, write_back: bool = True,
+                delta_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x += delta in place (if given; times the per-channel `delta_scale` if given), then return norm(x) in
+        `out_dtype`; `rows` picks rows of x."""
         raise NotImplementedError
 
 

@@ -11,7 +11,7 @@ from typing import Optional
 import torch
 
 from ..config.spec import LayerSpec
-from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, PendingNorm, build_part, register
+from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, Part, PendingNorm, TensorNeed, build_part, register
 
 
 class ResidualStream:
@@ -20,9 +20,12 @@ class ResidualStream:
     def __init__(self, x: torch.Tensor):
         self.x = x
         self.pending: Optional[torch.Tensor] = None
+        self.pending_scale: Optional[torch.Tensor] = None    # per-channel factor the pending output is added with
 
     def take_pending(self) -> Optional[torch.Tensor]:
+        """The pending output; whoever takes it adds it (times `pending_scale`, read before this call) to x."""
         pending, self.pending = self.pending, None
+        self.pending_scale = None
         return pending
 
 
@@ -47,3 +50,52 @@ class PreNormBlock:
         stream.pending = mixed
         h = PendingNorm(stream, self.feed_forward_norm, self.dtype)
         stream.pending = self.feed_forward.forward(h if self.feed_forward.accepts_pending_norm else h.materialize(), ctx)
+
+
+class ChannelScale(Part):
+    """One factor per channel (a layer scale).  params: size; weight_name."""
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        self.size = int(spec["size"])
+        self.weight_name = spec.get("weight_name", "")
+        self.weight = None
+
+    def tensor_needs(self):
+        return {self.weight_name: TensorNeed((self.size,), role="vector")}
+
+    def load(self, tensors):
+        self.weight = tensors[self.weight_name].float().contiguous()    # applied to a float output on its way into the float stream
+
+
+@register(ARRANGEMENTS, "pre_norm_scaled")
+class PreNormScaledBlock:
+    """x += s1 * mixer(norm1(x)); x += s2 * feed_forward(norm2(x)), with s1, s2 one factor per channel; the feed-forward
+    half may be absent.  The scaled add of each output is made by the norm kernel that follows it."""
+
+    def __init__(self, spec: LayerSpec, dtype: torch.dtype):
+        self.spec = spec
+        self.dtype = dtype
+        self.mixer_norm = build_part(NORMS, spec.mixer_norm, dtype, "norm")
+        self.mixer = build_part(MIXERS, spec.mixer, dtype, "mixer")
+        self.mixer_scale = ChannelScale(spec.extras["mixer_scale"], dtype)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_scale = None
+        if spec.feed_forward is not None:
+            self.feed_forward_norm = build_part(NORMS, spec.feed_forward_norm, dtype, "norm")
+            self.feed_forward = build_part(FEED_FORWARDS, spec.feed_forward, dtype, "feed-forward")
+            self.feed_forward_scale = ChannelScale(spec.extras["feed_forward_scale"], dtype)
+
+    def parts(self):
+        slots = ("mixer_norm", "mixer", "mixer_scale", "feed_forward_norm", "feed_forward", "feed_forward_scale")
+        return {slot: getattr(self, slot) for slot in slots if getattr(self, slot) is not None}
+
+    @staticmethod
+    def _run(part, h, *args):
+        return part.forward(h if part.accepts_pending_norm else h.materialize(), *args)
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        mixed = self._run(self.mixer, PendingNorm(stream, self.mixer_norm, self.dtype), ctx, cache)
+        stream.pending, stream.pending_scale = mixed, self.mixer_scale.weight
+        if self.feed_forward is not None:
+            out = self._run(self.feed_forward, PendingNorm(stream, self.feed_forward_norm, self.dtype), ctx)
+            stream.pending, stream.pending_scale = out, self.feed_forward_scale.weight

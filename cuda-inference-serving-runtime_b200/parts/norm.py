@@ -15,7 +15,7 @@ from .base import NORMS, Norm, TensorNeed, register
 
 @register(NORMS, "rms_norm")
 class RMSNorm(Norm):
-    """params: size (width), eps."""
+    """params: size (width), eps; weight_name (the tensor's name below the part's prefix, default "weight")."""
 
     fusable_into_product = True     # y = x * rsqrt(mean(x^2) + eps) * w is what the products' norm prologue computes
 
@@ -23,18 +23,20 @@ class RMSNorm(Norm):
         super().__init__(spec, dtype)
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
+        self.weight_name = spec.get("weight_name", "weight")
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_needs(self) -> Dict[str, TensorNeed]:
-        return {"weight": TensorNeed((self.size,), role="vector")}
+        return {self.weight_name: TensorNeed((self.size,), role="vector")}
 
     def load(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.weight_name]
 
     def kernel_jobs(self):
         return [("elementwise.cu", {}, ())]
 
-    def forward(self, x, delta, out_dtype, rows=None, write_back=True):
+    def forward(self, x, delta, out_dtype, rows=None, write_back=True, delta_scale=None):
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.size), dtype=out_dtype, device=x.device)
-        return kernels.add_rmsnorm(x, delta, self.weight, self.eps, out, rows=rows, write_back=write_back)
+        return kernels.add_rmsnorm(x, delta, self.weight, self.eps, out, rows=rows, write_back=write_back,
+                                   delta_scale=delta_scale)

@@ -50,6 +50,13 @@ class RotaryHalf(PositionEncoding):
         return cached
 
 
+@register(POSITIONS, "rotary_interleaved")
+class RotaryInterleaved(RotaryHalf):
+    """The same turn with neighbours paired: coordinates (2i, 2i + 1) turn by pos * theta^(-2i/dim).  params as above."""
+
+    interleaved = True
+
+
 @register(POSITIONS, "none")
 class NoPosition(PositionEncoding):
     def rotation(self, ctx):

@@ -41,7 +41,7 @@ def draw(name: str, need: TensorNeed, seed: int, device=None) -> torch.Tensor:
     values = torch.randn(shape, generator=gen, dtype=torch.float32, device=device if on_device else "cpu")
     if need.role == "vector":
         return 1.0 + VECTOR_STD * values
-    return MATRIX_STD * values
+    return (MATRIX_STD if need.init_std is None else need.init_std) * values
 
 
 def random_tensors(needs: Mapping[str, TensorNeed], seed: int, dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
