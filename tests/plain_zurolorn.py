@@ -9,11 +9,10 @@ them (operands of matrix products), so that the twin shows what storage alone co
 """
 from __future__ import annotations
 
-import math
-
 import torch
 
 F = torch.float64
+SCORE_LOG = None      # a list here receives (scores [T, experts], router settings) of every routing, in run order
 
 
 def rms_unit(x, eps):
@@ -23,10 +22,6 @@ def rms_unit(x, eps):
 
 def rms_norm(x, weight, eps):
     return rms_unit(x, eps) * weight
-
-
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
 
 
 def rotate(v, positions, base, dims, interleaved):
@@ -94,6 +89,8 @@ def route(h, router_w, router):
     the best `keep` groups stay open, the `top` best open experts are taken, weight = score * scale."""
     E, top = router["experts"], router["top"]
     s = torch.sigmoid(h @ router_w.to(F).T)                                   # [T, E]
+    if SCORE_LOG is not None:
+        SCORE_LOG.append((s, router))
     allowed = torch.ones_like(s, dtype=torch.bool)
     groups = router.get("groups")
     if groups:
