@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--preset smollm2-135m] [--batch 8] [--context 4096] [--dtype bfloat16] [--layers L]
-                    [--workload decode|mixed]
+                    [--workload decode|mixed] [--designs 1024,2048]
 
 Default run: the SmolLM2-135M layer sizes with seeded random weights, bfloat16, batch 8,
 every request holding about 4096 tokens of context while it decodes.  Prints ONE JSON line:
@@ -27,6 +27,8 @@ every request holding about 4096 tokens of context while it decodes.  Prints ONE
 --workload mixed: the continuous-batching workload (by default the SmolLM2-1.7B sizes, 64 requests with prompts
 of 128 to 2048 tokens, 256 generated tokens each) through the scheduler with graphs on; prints total, prefill
 and decode tokens per second, launch counts, graph statistics and a roofline for the whole run.
+--designs SIZES: Zurolorn (latent attention, routed experts) beside the Llama shape of equal size at the named widths:
+prompt and decode tokens per second of both, and per kind of kernel the device time and the distance from the roofline.
 --impl reference: the reference's own stock code on the same decode workload (see reference_arm).
 
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else 6.65 TB/s and
@@ -427,6 +429,157 @@ def kernel_rooflines(model, raw: dict, batch: int, context: int, seed: int, dtyp
     return out
 
 
+# ------------------------------------------------------------------ two designs side by side
+def design_pair(width: int, layers: int, heads: int, ff_active: int, experts: int, top: int, vocab: int = 32000):
+    """A Zurolorn shape and the Llama shape of equal size beside it: the same width, layers, query heads of 64 and
+    vocabulary; the experts a token uses together are as wide as the dense feed-forward."""
+    mixer = {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 96, "rot": {"base": 10000.0, "dims": 32}, "scale": 96 ** -0.5}
+    mlp = {"kind": "moe", "expert": {"ff": ff_active // top},
+           "router": {"experts": experts, "top": top, "scale": 1.0, "groups": {"count": 4, "keep": 2}}}
+    zur = {"architecture": "Zurolorn", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+           "logit_scale": 1.0, "max_positions": 8192,
+           "layers": [{"type": "latent_attention" if i % 2 else "latent_attention_2", "mixer": dict(mixer, q_rank=width // 4), "mlp": mlp}
+                      for i in range(layers)]}
+    llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu", "vocab_size": vocab, "hidden_size": width,
+             "intermediate_size": ff_active, "num_hidden_layers": layers, "num_attention_heads": heads, "num_key_value_heads": max(1, heads // 4),
+             "head_dim": 64, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 8192, "tie_word_embeddings": False}
+    return zur, llama
+
+
+DESIGN_SIZES = {"1024": (1024, 8, 16, 2048, 16, 4), "2048": (2048, 8, 32, 4096, 32, 4), "4096": (4096, 4, 32, 8192, 64, 8)}
+KERNEL_KIND = {   # which kernels of the two designs are alike
+    "gemm_tcgen05": "product, many tokens", "gemm_library": "product, many tokens", "gemm_tcgen05_swiglu": "feed-forward product, many tokens",
+    "gemm_tcgen05_rope": "product, many tokens", "gemm_tcgen05_grouped": "feed-forward product, many tokens", "skinny_gemm": "product, few tokens",
+    "moe_rows": "feed-forward product, few tokens", "gemm_heads": "product per head", "attn_prefill_wide": "prompt attention", "attn_prefill": "prompt attention",
+    "attn_decode": "decode attention", "merge_out_proj": "product, few tokens", "add_rmsnorm": "norm", "embedding": "row kernels", "rope_store": "row kernels",
+    "latent_rows": "row kernels", "latent_query": "row kernels", "latent_gate": "row kernels", "moe_router": "row kernels", "moe_gather": "row kernels",
+    "moe_combine": "row kernels", "moe_sort": "bookkeeping", "stream_add": "row kernels", "swiglu": "row kernels"}
+
+
+def generic_need(name: str, shape: tuple, cache_tokens: int, causal: int):
+    """(bytes, flops) a launch must move and do, from the kernel's name and the shape it was called with (bfloat16)."""
+    if name == "skinny_gemm":
+        tokens, n, k, epilogue, normed = shape
+        return n * k * 2 + tokens * k * (8 if normed else 2), 2.0 * tokens * n * k
+    if name in ("gemm_tcgen05", "gemm_tcgen05_swiglu", "gemm_tcgen05_rope", "gemm_library"):
+        m, n, k = shape
+        return (m * k + n * k) * 2 + m * n * (4 if name in ("gemm_tcgen05", "gemm_library") else 2), 2.0 * m * n * k
+    if name == "gemm_tcgen05_grouped":
+        m, groups, n, k, relu2 = shape
+        return (m * k + groups * n * k) * 2 + m * n * (2 if relu2 else 4), 2.0 * m * n * k
+    if name == "gemm_heads":
+        m, heads, a, b = shape
+        return heads * a * b * 2 + m * heads * (a + b) * 2, 2.0 * m * heads * a * b
+    if name == "moe_rows":
+        tokens, experts, ff, hidden, top = shape
+        return min(tokens * top, experts) * 2 * ff * hidden * 2, 4.0 * tokens * top * ff * hidden
+    if name == "merge_out_proj":
+        n_dec, n, k, splits = shape
+        return n * k * 2 + n_dec * splits * k * 4, 2.0 * n_dec * n * k
+    if name == "attn_decode":
+        n_dec, hq, hkv, d, merge, one_plane = shape
+        return cache_tokens * (1 if one_plane else 2) * hkv * d * 2, 4.0 * cache_tokens * hq * d
+    if name in ("attn_prefill_wide", "attn_prefill"):
+        tokens, hq, hkv, d = shape
+        return 2 * tokens * (hq + 2 * hkv) * d * 2, 4.0 * hq * d * causal * (causal + 1) / 2
+    if name == "add_rmsnorm":
+        rows, hidden, added = shape
+        return rows * hidden * (4 + (8 if added else 0) + 2), 0.0
+    if name in ("embedding", "stream_add"):
+        return shape[0] * shape[1] * 8, 0.0
+    if name in ("latent_rows", "latent_query", "rope_store"):
+        return shape[0] * shape[1] * 6, 0.0
+    if name == "latent_gate":
+        return shape[0] * shape[1] * 10, 0.0
+    if name == "moe_gather":
+        return shape[0] * shape[1] * 4, 0.0
+    if name == "moe_combine":
+        tokens, top, hidden = shape
+        return tokens * hidden * 4 * (top + 1), 0.0
+    if name == "moe_router":
+        tokens, experts, hidden = shape
+        return (tokens + experts) * hidden * 2, 2.0 * tokens * experts * hidden
+    return 0, 0.0
+
+
+def design_kernels(model, batch: int, context: int, prompt: int, seed: int, hbm_gbs: float, burst_tflops: float) -> dict:
+    """Per kind of kernel, for one decode step and one prompt: device time (each launch alone between two CUDA events) and how
+    far the kind is from its roofline (sum of the launches' target times over the sum of their times)."""
+    import numpy as np
+    import torch
+    from cisr_b200 import StepEntry, Stepper
+    from cisr_b200.ops import kernels
+
+    out = {}
+    rng = np.random.default_rng(seed + 3)
+    for phase in ("decode", "prefill"):
+        if phase == "decode":
+            stepper = Stepper(model, n_pages=batch * (-(-context // PAGE_SIZE) + 1), page_size=PAGE_SIZE, max_slots=batch)
+            keys = [f"k{i}" for i in range(batch)]
+            last = fill_requests(stepper, keys, context - 4, model.spec.vocab_size, seed)
+            stepper.step([StepEntry(k, [last[k]], [0]) for k in keys])
+            entries = [StepEntry(k, [last[k]], [0]) for k in keys]
+            cache_tokens, causal = batch * (context - 2), 0
+        else:
+            stepper = Stepper(model, n_pages=-(-prompt // PAGE_SIZE) + 1, page_size=PAGE_SIZE, max_slots=1)
+            ids = rng.integers(0, model.spec.vocab_size, size=prompt).tolist()
+            stepper.create("p"); stepper.step([StepEntry("p", ids, [prompt - 1])]); stepper.release("p")
+            stepper.create("p")
+            entries = [StepEntry("p", ids, [prompt - 1])]
+            cache_tokens, causal = 0, prompt
+        torch.cuda.synchronize()
+        torch.cuda._sleep(int(0.06 * 1.9e9))          # the host queues the whole step while the device idles
+        with kernels.timed_launches() as timed:
+            stepper.step(entries)
+        kinds = {}
+        for (name, shape), v in timed.summary().items():
+            need_bytes, need_flops = generic_need(name, shape, cache_tokens, causal)
+            target_us = max(need_bytes / (hbm_gbs * 1e9), need_flops / (burst_tflops * 1e12)) * 1e6 * v["launches"]
+            entry = kinds.setdefault(KERNEL_KIND.get(name, name), {"launches": 0, "us": 0.0, "target_us": 0.0, "kernels": set()})
+            entry["launches"] += v["launches"]; entry["us"] += v["us"]; entry["target_us"] += target_us; entry["kernels"].add(name)
+        total = sum(e["us"] for e in kinds.values())
+        out[phase] = {kind: {"launches": e["launches"], "us": round(e["us"], 1), "share": round(e["us"] / total, 3),
+                             "frac_of_roofline": round(e["target_us"] / e["us"], 4) if e["us"] > 0 else None, "kernels": sorted(e["kernels"])}
+                      for kind, e in sorted(kinds.items(), key=lambda kv: -kv[1]["us"])}
+        out[phase + "_sum_us"] = round(total, 1)
+        del stepper
+        torch.cuda.empty_cache()
+    return out
+
+
+def design_comparison(args, hbm_gbs: float, burst_tflops: float, peak_source: str) -> int:
+    """--designs: prompt and decode throughput of Zurolorn beside the Llama shape of equal size (seeded random weights), and per
+    kind of kernel the distance from the roofline in both.  One JSON line."""
+    import torch
+    from cisr_b200 import Model
+
+    sizes = [s for s in args.designs.split(",") if s]
+    batch, context, prompt = args.batch, min(args.context, 2048), PREFILL_TOKENS
+    line = {"designs": "zurolorn beside llama at equal size", "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
+            "batch": batch, "context": context, "prompt_tokens": prompt, "peaks": peak_source, "sizes": {}}
+    sampler = ClockSampler().start()
+    for size in sizes:
+        if size not in DESIGN_SIZES:
+            raise SystemExit(f"--designs takes sizes from {', '.join(DESIGN_SIZES)}")
+        width, layers, heads, ff_active, experts, top = DESIGN_SIZES[size]
+        entry = {"width": width, "layers": layers, "heads": heads, "feed_forward_active": ff_active, "experts": experts, "top": top}
+        for name, raw in zip(("zurolorn", "llama"), design_pair(width, layers, heads, ff_active, experts, top)):
+            model = Model.from_config(raw, seed=args.seed, dtype="bfloat16")
+            prefill_ms = prefill_run(model, prompt, args.seed)
+            d = device_decode(model, batch, context, min(args.steps, 64), args.warmup, args.seed, min_seconds=0.2)
+            entry[name] = {"prefill_tokens_per_s": round(prompt / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                           "decode_tokens_per_s": round(d["value"], 1), "decode_ms_per_step": round(d["ms_per_step"], 4),
+                           "launches_per_decode_step": d["launches"]}
+            if not args.no_kernels:
+                entry[name]["kernels"] = design_kernels(model, batch, context, prompt, args.seed, hbm_gbs, burst_tflops)
+            del model
+            torch.cuda.empty_cache()
+        line["sizes"][size] = entry
+    line["clocks"] = sampler.stop()
+    print(json.dumps(line))
+    return 0
+
+
 # ------------------------------------------------------------------ the continuous-batching workload
 def mixed_workload(model, raw: dict, layers: int, args, hbm_gbs: float, bf16_tflops: float) -> dict:
     """`--requests` requests with prompts uniform in [128, 2048] and `--new-tokens` generated tokens each, all queued at
@@ -661,6 +814,9 @@ def main() -> int:
     parser.add_argument("--new-tokens", type=int, default=256, help="--workload mixed: tokens generated per request")
     parser.add_argument("--token-budget", type=int, default=2048, help="--workload mixed: tokens per step")
     parser.add_argument("--no-kernels", action="store_true", help="skip the per-kernel figures")
+    parser.add_argument("--designs", metavar="SIZES", default=None,
+                        help="instead of the default workload: Zurolorn beside the Llama shape of equal size, prompt and decode, at "
+                             "the named widths (comma-separated, from 1024, 2048, 4096)")
     args = parser.parse_args()
     if args.workload == "mixed" and "--preset" not in " ".join(sys.argv):
         args.preset = "smollm2-1.7b"
@@ -680,6 +836,8 @@ def main() -> int:
     import torch
 
     hbm_gbs, bf16_tflops, bf16_burst, peak_source = peaks()
+    if args.designs:
+        return design_comparison(args, hbm_gbs, bf16_burst, peak_source)
     model, raw, full_layers = make_model(args)
     layers = raw["num_hidden_layers"]
     dtype_bytes = 2 if args.dtype == "bfloat16" else 4

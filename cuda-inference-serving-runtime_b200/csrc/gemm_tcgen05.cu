@@ -27,7 +27,7 @@
 
 namespace {
 typedef __nv_bfloat16 bf16;
-enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ROPE = 2 };
+enum : int { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ROPE = 2, EPI_RELU2 = 3 };
 constexpr int BK = 64, UMMA_K = 16;     // BM = 128 (tcgen05.cuh)
 
 struct Epilogue {                       // what the epilogue variants need beyond the accumulator
@@ -35,6 +35,10 @@ struct Epilogue {                       // what the epilogue variants need beyon
     int accumulate;                     // PLAIN: out += product (the residual stream, in place) instead of out = product
     const float* cos_t; const float* sin_t; bf16* q_out; bf16* k_cache; bf16* v_cache; const int* positions;
     const int* token_req; const int* req_slot; const int* block_table; int table_width; int page_size; int hq; int hkv; int dim;
+    // Grouped product: the rows of `a` are sorted by group (an expert), each group's rows padded to whole 128-row tiles;
+    // tile_group[i] is the group of row tile i (-1: the tile holds no rows and is skipped), and group g multiplies with
+    // rows [g * n, (g + 1) * n) of `w`.  Null: one weight matrix for all rows.
+    const int* tile_group;
 };
 // 32 floats -> 32 bfloat16 (64 bytes) at dst; `count` of them are valid
 __device__ __forceinline__ void store_bf16x32(bf16* dst, const float (&v)[32], int count) {
@@ -100,6 +104,17 @@ __device__ __forceinline__ void epilogue_tile(const Epilogue& ep, uint32_t lane_
                         if (n0 + c + j < n) dst[j] = ep.accumulate ? dst[j] + __uint_as_float(v[j]) : __uint_as_float(v[j]);
                 }
             }
+        }
+    } else if (EPI == EPI_RELU2) {
+        // out = max(product, 0)^2 as bfloat16 [m, n]: the activation of an expert's first product
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+            uint32_t v[32];
+            tmem_load32(lane_base + (uint32_t)c, v);
+            float act[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) { const float r = fmaxf(__uint_as_float(v[j]), 0.f); act[j] = r * r; }
+            if (row < m && n0 + c < n) store_bf16x32(ep.out_bf16 + (size_t)row * n + n0 + c, act, n - (n0 + c));
         }
     } else if (EPI == EPI_SWIGLU) {
 #pragma unroll 1
@@ -216,8 +231,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             };
             // The weights do not come from the kernel before this one: the first stages' weight tiles are requested
             // before the wait on that kernel, the activation tiles after it.
-            const int early = k_blocks < STAGES ? k_blocks : STAGES;
-            if ((int)blockIdx.x < total_tiles) {
+            // (a grouped product learns its weight rows from the kernel before: nothing is requested early)
+            const int early = ep.tile_group ? 0 : (k_blocks < STAGES ? k_blocks : STAGES);
+            if (early && (int)blockIdx.x < total_tiles) {
                 const int n0 = ((int)blockIdx.x / tiles_m) * TILE_N;
                 for (int kb = 0; kb < early; ++kb) {
                     mbar_expect_tx(full_bar + kb, (uint32_t)(S::A_BYTES + S::B_BYTES));
@@ -229,6 +245,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int kbg = 0;                                                      // k blocks issued so far, over all tiles
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;   // neighbours share the weight tile
+                int w_row = n0;
+                if (ep.tile_group) {
+                    const int group = ep.tile_group[tile % tiles_m];
+                    if (group < 0) continue;
+                    w_row = group * n + n0;
+                }
                 for (int kb = 0; kb < k_blocks; ++kb, ++kbg) {
                     const int s = kbg % STAGES;
                     if (kbg < early) {        // this stage's barrier is armed and its weight tile on the way already
@@ -239,7 +261,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (!ok) break;
                     mbar_expect_tx(full_bar + s, (uint32_t)(S::A_BYTES + S::B_BYTES));
                     tma_load_2d(tiles + s * (S::A_BYTES + S::B_BYTES), &map_a, kb * BK, m0, full_bar + s);
-                    load_b(s, kb, n0);
+                    load_b(s, kb, w_row);
                 }
             }
         }
@@ -247,7 +269,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(BN);
             int kbg = 0, it = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+            if (ep.tile_group) pdl_wait();      // the tile list comes from the kernel before
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (ep.tile_group && ep.tile_group[tile % tiles_m] < 0) continue;      // an empty row tile: skipped by every role alike
                 const int acc = it & 1;
                 ok = mbar_wait(acc_empty + acc, ((it >> 1) & 1) ^ 1);          // the epilogue has drained this buffer
                 if (!ok) break;
@@ -266,13 +290,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     umma_commit(empty_bar + s);                                // frees the stage when these MMAs finish
                 }
                 if (ok) umma_commit(acc_full + acc);                           // the whole tile is accumulated
+                ++it;
             }
         }
     } else {
         const int quarter = warp & 3;                                          // the 32 lanes this warp may read
         int it = 0;
         pdl_wait();      // outputs may alias what the kernel before still reads; step metadata is older than that kernel
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            if (ep.tile_group && ep.tile_group[tile % tiles_m] < 0) continue;
             const int acc = it & 1;
             const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * TILE_N;
             const int row = m0 + quarter * 32 + lane;
@@ -291,6 +317,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(acc_empty + acc)) : "memory");
+            ++it;
         }
     }
     if (!ok && lane == 0) atomicExch(error, 1);
@@ -304,11 +331,11 @@ bool g_pdl = false;
 int* g_error = nullptr;          // device flag, owned by the caller (see cisr_gemm_tcgen05_init)
 
 template <int BN, int STAGES, int EPI>
-int launch(const void* a, const void* w, const Epilogue& ep, int m, int n, int k, int tiles_n, cudaStream_t s) {
+int launch(const void* a, const void* w, const Epilogue& ep, int m, int n, int k, int tiles_n, cudaStream_t s, int groups = 1) {
     CUtensorMap map_a, map_w;
     int status = cached_map(&map_a, a, m, k, BM);
     if (status) return status;
-    if ((status = cached_map(&map_w, w, n, k, EPI == EPI_SWIGLU ? BN / 2 : BN))) return status;
+    if ((status = cached_map(&map_w, w, (long long)groups * n, k, EPI == EPI_SWIGLU ? BN / 2 : BN))) return status;
     typedef Smem<BN, STAGES> S;
     static bool configured = false;
     if (!configured) {
@@ -431,4 +458,26 @@ CISR_EXPORT int cisr_gemm_tcgen05_rope(const void* a, const void* w, int m, int 
     if (deep == 64 && dim == 64) return launch<64, 8, EPI_ROPE>(a, w, ep, m, n, k, (n + 63) / 64, (cudaStream_t)stream);   // a whole head per tile
     if (deep) return launch<128, 6, EPI_ROPE>(a, w, ep, m, n, k, (n + 127) / 128, (cudaStream_t)stream);
     return launch<128, 3, EPI_ROPE>(a, w, ep, m, n, k, (n + 127) / 128, (cudaStream_t)stream);
+}
+
+// The product of rows sorted by group with each group's own weight matrix: a [m, k] with every group's rows padded to
+// whole 128-row tiles, w [groups * n, k] (group g's matrix in rows g * n ..), tile_group [m / 128] as described at
+// `Epilogue::tile_group`.  relu2 == 0: out is float [m, n] = a_g w_g^T; else out is bfloat16 [m, n] = max(a_g w_g^T, 0)^2.
+CISR_EXPORT int cisr_gemm_tcgen05_grouped(const void* a, const void* w, void* out, int m, int n, int k, int groups,
+                                          const int* tile_group, int relu2, void* stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (!g_encode || !g_error) return -13;
+    if (!operands_ok(a, w, k) || ((uintptr_t)out & 15) || m % BM || !tile_group || groups <= 0) return -2;
+    Epilogue ep = {};
+    ep.tile_group = tile_group;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool wide = wide_tiles(m, (n + 255) / 256);
+    if (relu2) {
+        ep.out_bf16 = (bf16*)out;
+        if (wide) return launch<256, 4, EPI_RELU2>(a, w, ep, m, n, k, (n + 255) / 256, s, groups);
+        return launch<128, 3, EPI_RELU2>(a, w, ep, m, n, k, (n + 127) / 128, s, groups);
+    }
+    ep.out_f32 = (float*)out;
+    if (wide) return launch<256, 4, EPI_PLAIN>(a, w, ep, m, n, k, (n + 255) / 256, s, groups);
+    return launch<128, 3, EPI_PLAIN>(a, w, ep, m, n, k, (n + 127) / 128, s, groups);
 }

@@ -7,8 +7,11 @@
 //   the `top` best open experts are chosen, weight = s * route_scale (not renormalised)
 //   y = sum over chosen e of weight_e * W_down_e act(W_up_e h),   act(z) = max(z, 0)^2
 //
-// The expert products here: a warp per output feature, each chosen expert's rows streamed once per token that chose it
-// (moe_up_rows / moe_down_rows).
+// Two shapes of the expert products.  Few tokens (and the float path): a warp per output feature, each chosen expert's
+// rows streamed once per token that chose it (moe_up_rows / moe_down_rows).  Many tokens in bfloat16: the pairs are
+// sorted by expert on the device (moe_sort), the activations gathered into that order (moe_gather), the two products run
+// as grouped tcgen05 products (gemm_tcgen05.cu, the first with the activation as its epilogue), and each token's rows
+// are summed with the router's weights (moe_combine).
 #include "common.cuh"
 
 static bool g_pdl = false;
@@ -174,4 +177,90 @@ CISR_EXPORT int cisr_moe_rows(const void* h, const void* w_up, const void* w_dow
     if (st) return st;
     return launch_kernel(moe_down_rows_kernel<float>, down_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl, (const float*)act,
                          (const float*)w_down, chosen, weight, hidden, ff, top, out);
+}
+
+// ---------------------------------------------------------------- many tokens: rows sorted by expert
+// The (token, chosen expert) pairs of a step are laid out expert by expert, each expert's rows padded to whole tiles of
+// `tile` rows, so that one grouped product serves all experts:
+//   row_of[pair]        the row of pair t * top + k in the sorted layout
+//   src_token[row]      the token whose activations row `row` holds, -1 for padding (and for rows beyond the last tile used)
+//   tile_group[i]       the expert of row tile i, -1 for tiles beyond the last one used
+// One CTA; shared memory: 3 * n_experts ints.  Which row inside its expert's block a pair gets depends on the order the
+// atomics happen to run in; every row is computed by itself and a token's experts are summed in the router's order, so
+// the result does not.
+__global__ void moe_sort_kernel(const int* __restrict__ chosen, int n_pairs, int top, int n_experts, int tile, int max_rows,
+                                int* __restrict__ row_of, int* __restrict__ src_token, int* __restrict__ tile_group) {
+    extern __shared__ int sort_smem[];
+    int* count = sort_smem;
+    int* offset = sort_smem + n_experts;
+    int* fill = sort_smem + 2 * n_experts;
+    pdl_trigger();
+    pdl_wait();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) { count[e] = 0; fill[e] = 0; }
+    for (int r = threadIdx.x; r < max_rows; r += blockDim.x) src_token[r] = -1;
+    for (int i = threadIdx.x; i < max_rows / tile; i += blockDim.x) tile_group[i] = -1;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&count[chosen[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < n_experts; ++e) { offset[e] = at; at += (count[e] + tile - 1) / tile * tile; }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x)
+        for (int i = offset[e] / tile; i < (offset[e] + count[e] + tile - 1) / tile; ++i) tile_group[i] = e;
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = chosen[p];
+        const int row = offset[e] + atomicAdd(&fill[e], 1);
+        row_of[p] = row;
+        src_token[row] = p / top;
+    }
+}
+
+// sorted[row, :] = h[src_token[row], :], zeros where src_token[row] < 0.  16-byte copies (hidden * 2 bytes % 16 == 0).
+__global__ void moe_gather_kernel(const uint4* __restrict__ h, const int* __restrict__ src_token, uint4* __restrict__ sorted, int row_vec) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x, src = src_token[row];
+    for (int i = threadIdx.x; i < row_vec; i += blockDim.x)
+        sorted[(size_t)row * row_vec + i] = src >= 0 ? h[(size_t)src * row_vec + i] : make_uint4(0, 0, 0, 0);
+}
+
+// out[t, c] = sum_k weight[t, k] * sorted_out[row_of[t * top + k], c], k in the router's order.
+__global__ void moe_combine_kernel(const float* __restrict__ sorted_out, const int* __restrict__ row_of, const float* __restrict__ weight,
+                                   int top, int hidden, float* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) acc += weight[(size_t)t * top + k] * sorted_out[(size_t)row_of[(size_t)t * top + k] * hidden + c];
+        out[(size_t)t * hidden + c] = acc;
+    }
+}
+
+CISR_EXPORT int cisr_moe_sort(const int* chosen, int tokens, int top, int n_experts, int tile, int max_rows, int* row_of,
+                              int* src_token, int* tile_group, void* stream) {
+    if (tokens <= 0) return 0;
+    // the padded blocks of all experts together: at most pairs + (experts in use) * (tile - 1) rows, in whole tiles
+    const long long pairs = (long long)tokens * top, in_use = pairs < n_experts ? pairs : n_experts;
+    if (tile <= 0 || max_rows % tile || max_rows < (pairs + in_use * (tile - 1)) / tile * tile) return -2;
+    const size_t smem = (size_t)3 * n_experts * sizeof(int);
+    if (smem > 48 * 1024) return -3;
+    return launch_kernel(moe_sort_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)stream, g_pdl, chosen, tokens * top, top, n_experts, tile,
+                         max_rows, row_of, src_token, tile_group);
+}
+
+CISR_EXPORT int cisr_moe_gather(const void* h, const int* src_token, void* sorted, int rows, int hidden, void* stream) {
+    if (rows <= 0) return 0;
+    if ((hidden * 2) % 16 || (((uintptr_t)h | (uintptr_t)sorted) & 15)) return -2;
+    return launch_kernel(moe_gather_kernel, dim3(rows), dim3(128), 0, (cudaStream_t)stream, g_pdl, (const uint4*)h, src_token, (uint4*)sorted,
+                         hidden * 2 / 16);
+}
+
+CISR_EXPORT int cisr_moe_combine(const float* sorted_out, const int* row_of, const float* weight, int tokens, int top, int hidden,
+                                 float* out, void* stream) {
+    if (tokens <= 0) return 0;
+    return launch_kernel(moe_combine_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, g_pdl, sorted_out, row_of, weight, top,
+                         hidden, out);
 }

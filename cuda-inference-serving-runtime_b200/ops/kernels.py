@@ -535,7 +535,7 @@ def _moe():
     lib = _moe_state.get("lib")
     if lib is None:
         lib = load_library("moe.cu")
-        for name in ("cisr_moe_router", "cisr_moe_rows"):
+        for name in ("cisr_moe_router", "cisr_moe_rows", "cisr_moe_sort", "cisr_moe_gather", "cisr_moe_combine"):
             getattr(lib, name).restype = ctypes.c_int
         lib.cisr_moe_set_pdl(int(_pdl_state["on"]))
         _moe_state["lib"] = lib
@@ -573,6 +573,81 @@ def moe_rows(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: 
     _check(_moe().cisr_moe_rows(_p(h), _p(w_up), _p(w_down), dtype_code(h.dtype), _p(chosen), _p(weight), tokens, hidden, ff, top,
                                 _p(act), _p(out), _stream()), "moe_rows", own=2)
     return out
+
+
+MOE_TILE = 128                   # rows per tile of the grouped product: each expert's rows are padded to whole tiles
+MOE_GROUPED_MIN_ROWS = 64        # (token, expert) pairs per expert, on average, from which sorting and the grouped product pay
+
+
+def moe_grouped_ok(h: torch.Tensor, w_up: torch.Tensor, top: int) -> bool:
+    """Whether a step's experts run as grouped tcgen05 products: bfloat16, widths whose rows are 16-byte multiples, and
+    enough pairs per expert that whole 128-row tiles are mostly real rows."""
+    experts, ff, hidden = w_up.shape
+    return (h.dtype == torch.bfloat16 and hidden % 8 == 0 and ff % 8 == 0 and h.shape[0] * top >= MOE_GROUPED_MIN_ROWS * experts
+            and h.shape[0] >= TCGEN05_MIN_TOKENS)
+
+
+def moe_sorted_rows(tokens: int, top: int, experts: int) -> int:
+    """Rows of the sorted layout: every expert's block padded to whole tiles, in the worst case."""
+    pairs = tokens * top
+    return max(MOE_TILE, (pairs + min(pairs, experts) * (MOE_TILE - 1)) // MOE_TILE * MOE_TILE)
+
+
+def moe_sort(chosen: torch.Tensor, experts: int, row_of: torch.Tensor, src_token: torch.Tensor, tile_group: torch.Tensor) -> None:
+    """Lay the (token, chosen expert) pairs out expert by expert, each expert's rows padded to whole tiles of MOE_TILE:
+    row_of[pair] = its row, src_token[row] = the token of that row (-1: padding), tile_group[tile] = its expert (-1: unused)."""
+    _need(chosen, torch.int32, "chosen", 2)
+    for name, t in (("row_of", row_of), ("src_token", src_token), ("tile_group", tile_group)):
+        _need(t, torch.int32, name, 1)
+    tokens, top = chosen.shape
+    rows = src_token.numel()
+    if row_of.numel() != tokens * top or rows % MOE_TILE or tile_group.numel() != rows // MOE_TILE:
+        raise KernelError("moe_sort: shapes disagree")
+    _check(_moe().cisr_moe_sort(_p(chosen), tokens, top, experts, MOE_TILE, rows, _p(row_of), _p(src_token), _p(tile_group), _stream()),
+           "moe_sort")
+
+
+def moe_gather(h: torch.Tensor, src_token: torch.Tensor, sorted_h: torch.Tensor) -> torch.Tensor:
+    """sorted_h[row] = h[src_token[row]], zeros where src_token[row] < 0 (bfloat16 rows of 16-byte multiples)."""
+    _need(h, torch.bfloat16, "h", 2); _need(sorted_h, torch.bfloat16, "sorted_h", 2); _need(src_token, torch.int32, "src_token", 1)
+    if sorted_h.shape != (src_token.numel(), h.shape[1]):
+        raise KernelError("moe_gather: shapes disagree")
+    _check(_moe().cisr_moe_gather(_p(h), _p(src_token), _p(sorted_h), sorted_h.shape[0], h.shape[1], _stream()), "moe_gather")
+    return sorted_h
+
+
+def moe_combine(sorted_out: torch.Tensor, row_of: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum over k of weight[t, k] * sorted_out[row_of[t * top + k]], in the order of k."""
+    _need(sorted_out, torch.float32, "sorted_out", 2); _need(row_of, torch.int32, "row_of", 1); _need(weight, torch.float32, "weight", 2)
+    _need(out, torch.float32, "out", 2)
+    tokens, top = weight.shape
+    if row_of.numel() != tokens * top or out.shape != (tokens, sorted_out.shape[1]):
+        raise KernelError("moe_combine: shapes disagree")
+    _check(_moe().cisr_moe_combine(_p(sorted_out), _p(row_of), _p(weight), tokens, top, out.shape[1], _p(out), _stream()), "moe_combine")
+    return out
+
+
+def moe_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
+                out: torch.Tensor) -> torch.Tensor:
+    """The same sum as `moe_rows` for many tokens: pairs sorted by expert on the device, activations gathered into that
+    order, both products as grouped tcgen05 products (relu^2 as the first one's epilogue), rows summed per token with the
+    router's weights in the router's order.  Nothing is read back to the host."""
+    _need(w_up, torch.bfloat16, "w_up", 3); _need(w_down, torch.bfloat16, "w_down", 3)
+    tokens, hidden = h.shape
+    experts, ff, _ = w_up.shape
+    top = chosen.shape[1]
+    if w_up.shape[2] != hidden or w_down.shape != (experts, hidden, ff) or out.shape != (tokens, hidden) or weight.shape != chosen.shape:
+        raise KernelError("moe_grouped: shapes disagree")
+    rows = moe_sorted_rows(tokens, top, experts)
+    device = h.device
+    row_of = torch.empty(tokens * top, dtype=torch.int32, device=device)
+    src_token = torch.empty(rows, dtype=torch.int32, device=device)
+    tile_group = torch.empty(rows // MOE_TILE, dtype=torch.int32, device=device)
+    moe_sort(chosen, experts, row_of, src_token, tile_group)
+    sorted_h = moe_gather(h, src_token, torch.empty((rows, hidden), dtype=torch.bfloat16, device=device))
+    act = gemm_tcgen05_grouped(sorted_h, w_up, torch.empty((rows, ff), dtype=torch.bfloat16, device=device), tile_group)
+    sorted_out = gemm_tcgen05_grouped(act, w_down, torch.empty((rows, hidden), dtype=torch.float32, device=device), tile_group)
+    return moe_combine(sorted_out, row_of, weight, out)
 
 
 # ------------------------------------------------------------------ sampling
@@ -860,6 +935,7 @@ def _tcgen05():
         lib.cisr_gemm_tcgen05.restype = ctypes.c_int
         lib.cisr_gemm_tcgen05_swiglu.restype = ctypes.c_int
         lib.cisr_gemm_tcgen05_rope.restype = ctypes.c_int
+        lib.cisr_gemm_tcgen05_grouped.restype = ctypes.c_int
         _check(lib.cisr_gemm_tcgen05_init(_p(_error_flag())), "tcgen05 gemm init", own=0)
         lib.cisr_gemm_tcgen05_set_pdl(int(_pdl_state["on"]))
         _tcgen05_state["lib"] = lib
@@ -901,6 +977,20 @@ def gemm_tcgen05_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> 
     if w.shape != (2 * inter, k) or out.shape[0] != m:
         raise KernelError(f"gemm swiglu: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
     _check(_tcgen05().cisr_gemm_tcgen05_swiglu(_p(a), _p(w), _p(out), m, inter, k, _stream()), "gemm_tcgen05_swiglu")
+    return out
+
+
+def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor) -> torch.Tensor:
+    """Rows of `a` (bfloat16 [M, K], M a multiple of 128) sorted by group, each 128-row tile with its group's matrix
+    w[g] (w bfloat16 [groups, N, K]; tile_group int32 [M / 128], -1: skip the tile).  out float [M, N]: the products;
+    out bfloat16 [M, N]: max(product, 0)^2."""
+    _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 3); _need(out, None, "out", 2); _need(tile_group, torch.int32, "tile_group", 1)
+    m, k = a.shape
+    groups, n, _ = w.shape
+    if w.shape[2] != k or out.shape != (m, n) or m % 128 or tile_group.numel() != m // 128 or out.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError(f"gemm grouped: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
+    _check(_tcgen05().cisr_gemm_tcgen05_grouped(_p(a), _p(w), _p(out), m, n, k, groups, _p(tile_group),
+                                                int(out.dtype == torch.bfloat16), _stream()), "gemm_tcgen05_grouped")
     return out
 
 
@@ -1000,7 +1090,11 @@ _DESCRIBE = {
     "latent_query": lambda q, *a, **kw: (int(q.shape[0]), int(q.shape[1])),
     "latent_gate": lambda values, *a, **kw: (int(values.shape[0]), int(values.shape[1])),
     "moe_router": lambda h, w, *a, **kw: (int(h.shape[0]), int(w.shape[0]), int(w.shape[1])),
-    "moe_rows": lambda h, w_up, *a, **kw: (int(h.shape[0]), int(w_up.shape[0]), int(w_up.shape[1]), int(w_up.shape[2])),
+    "moe_rows": lambda h, w_up, w_down, chosen, *a, **kw: (int(h.shape[0]), int(w_up.shape[0]), int(w_up.shape[1]), int(w_up.shape[2]), int(chosen.shape[1])),
+    "moe_sort": lambda chosen, experts, *a: (int(chosen.shape[0]), int(chosen.shape[1]), int(experts)),
+    "moe_gather": lambda h, src_token, sorted_h: (int(sorted_h.shape[0]), int(sorted_h.shape[1])),
+    "moe_combine": lambda sorted_out, row_of, weight, out: (int(out.shape[0]), int(weight.shape[1]), int(out.shape[1])),
+    "gemm_tcgen05_grouped": lambda a, w, out, tile_group: (int(a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2]), out.dtype == torch.bfloat16),
     "gemm_heads": lambda a, w, out, w_is_nk: (int(a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2])),
     "swiglu": lambda gate_up, out: (int(out.shape[0]), int(out.shape[1])),
     "rotary_tables": lambda positions, inv_freq, cos, sin: (int(cos.shape[0]), int(cos.shape[1])),
@@ -1010,7 +1104,7 @@ _DESCRIBE = {
     "attn_prefill_wide": lambda q, out, k_cache, *rest, **kw: (int(q.shape[0]), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2])),
     "attn_prefill": lambda q, out, k_cache, *rest, **kw: (int(q.shape[0]), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2])),
     "attn_decode": lambda q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec, *rest, **kw:
-        (int(n_dec), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2]), bool(kw.get("merge", True))),
+        (int(n_dec), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2]), bool(kw.get("merge", True)), k_cache.data_ptr() == v_cache.data_ptr()),
     "merge_out_proj": lambda partial, stats, n_splits, dec_req, q_start, n_dec, hq, dim, w, out, **kw:
         (int(n_dec), int(w.shape[0]), int(w.shape[1]), int(n_splits)),
     "sample": lambda logits, *rest, **kw: (int(logits.shape[0]), int(logits.shape[1])),

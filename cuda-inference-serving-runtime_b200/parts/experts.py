@@ -62,7 +62,7 @@ class RoutedExperts(FeedForward):
         self.down = torch.stack([tensors[self.names["down"].format(e)] for e in range(self.experts)]).contiguous()
 
     def kernel_jobs(self):
-        return kernels.moe_jobs()
+        return kernels.moe_jobs() + (kernels.tcgen05_jobs() if self.dtype == torch.bfloat16 else [])
 
     def route(self, h: torch.Tensor):
         """(chosen experts int32 [tokens, top], best first; their weights float [tokens, top])."""
@@ -75,6 +75,8 @@ class RoutedExperts(FeedForward):
     def forward(self, h, ctx):
         tokens = h.shape[0]
         chosen, weight = self.route(h)
-        act = torch.empty((tokens * self.top, self.ff), dtype=self.dtype, device=h.device)
         out = torch.empty((tokens, self.hidden), dtype=torch.float32, device=h.device)
+        if kernels.moe_grouped_ok(h, self.up, self.top):
+            return kernels.moe_grouped(h, self.up, self.down, chosen, weight, out)     # many tokens: sorted by expert, tcgen05
+        act = torch.empty((tokens * self.top, self.ff), dtype=self.dtype, device=h.device)
         return kernels.moe_rows(h, self.up, self.down, chosen, weight, act, out)

@@ -86,7 +86,8 @@ def test_router_kernel(dtype, experts, top, groups, keep, hidden):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("tokens, experts, top, ff, hidden", [(1, 4, 2, 40, 72), (13, 8, 3, 96, 128), (150, 6, 1, 24, 64), (300, 16, 4, 64, 192)])
+@pytest.mark.parametrize("tokens, experts, top, ff, hidden", [(1, 4, 2, 40, 72), (13, 8, 3, 96, 128), (150, 6, 1, 24, 64), (300, 16, 4, 64, 192),
+                                                              (700, 5, 2, 200, 328), (3, 40, 2, 136, 72)])
 def test_expert_kernels(dtype, tokens, experts, top, ff, hidden):
     from cisr_b200.ops import kernels
     g = torch.Generator().manual_seed(tokens)
@@ -106,6 +107,14 @@ def test_expert_kernels(dtype, tokens, experts, top, ff, hidden):
     kernels.moe_rows(h.cuda(), up.cuda(), down.cuda(), chosen.cuda(), weight.cuda(), act, out)
     err = (out.cpu().to(F) - want).abs().max() / want.abs().max()
     assert err < (2e-6 if dtype == torch.float32 else 8e-3), f"relative error {err:.2e}"
+    if dtype == torch.bfloat16 and hidden % 8 == 0 and ff % 8 == 0:
+        # the same sum by the path for many tokens: sorted by expert, grouped tensor-core products (here also with experts
+        # that no token chose, blocks of one row, and row tiles that stay unused)
+        grouped = torch.full((tokens, hidden), 7.0, dtype=torch.float32, device="cuda")
+        kernels.moe_grouped(h.cuda(), up.cuda(), down.cuda(), chosen.cuda(), weight.cuda(), grouped)
+        err = (grouped.cpu().to(F) - want).abs().max() / want.abs().max()
+        assert err < 8e-3, f"grouped products: relative error {err:.2e}"
+        kernels.raise_if_kernel_gave_up()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
