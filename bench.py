@@ -452,7 +452,8 @@ KERNEL_KIND = {   # which kernels of the two designs are alike
     "gemm_tcgen05_rope": "product, many tokens", "gemm_tcgen05_grouped": "feed-forward product, many tokens", "skinny_gemm": "product, few tokens",
     "moe_rows": "feed-forward product, few tokens", "gemm_heads": "product per head", "attn_prefill_wide": "prompt attention", "attn_prefill": "prompt attention",
     "attn_decode": "decode attention", "merge_out_proj": "product, few tokens", "add_rmsnorm": "norm", "embedding": "row kernels", "rope_store": "row kernels",
-    "latent_rows": "row kernels", "latent_query": "row kernels", "latent_gate": "row kernels", "moe_router": "row kernels", "moe_gather": "row kernels",
+    "latent_rows": "row kernels", "latent_query": "row kernels", "latent_gate": "row kernels", "latent_absorb": "product per head",
+    "latent_values": "product per head", "moe_router": "row kernels", "moe_gather": "row kernels",
     "moe_combine": "row kernels", "moe_sort": "bookkeeping", "stream_add": "row kernels", "swiglu": "row kernels"}
 
 
@@ -470,6 +471,12 @@ def generic_need(name: str, shape: tuple, cache_tokens: int, causal: int):
     if name == "gemm_heads":
         m, heads, a, b = shape
         return heads * a * b * 2 + m * heads * (a + b) * 2, 2.0 * m * heads * a * b
+    if name == "latent_absorb":
+        tokens, heads, a, b = shape
+        return heads * a * b * 2 + tokens * heads * (4 * a + 2 * b), 2.0 * tokens * heads * a * b
+    if name == "latent_values":
+        tokens, heads, a, b = shape
+        return heads * a * b * 2 + tokens * heads * (a + b) * 2, 2.0 * tokens * heads * a * b
     if name == "moe_rows":
         tokens, experts, ff, hidden, top = shape
         return min(tokens * top, experts) * 2 * ff * hidden * 2, 4.0 * tokens * top * ff * hidden
@@ -531,10 +538,12 @@ def design_kernels(model, batch: int, context: int, prompt: int, seed: int, hbm_
         torch.cuda._sleep(int(0.06 * 1.9e9))          # the host queues the whole step while the device idles
         with kernels.timed_launches() as timed:
             stepper.step(entries)
-        kinds = {}
+        kinds, detail = {}, {}
         for (name, shape), v in timed.summary().items():
             need_bytes, need_flops = generic_need(name, shape, cache_tokens, causal)
             target_us = max(need_bytes / (hbm_gbs * 1e9), need_flops / (burst_tflops * 1e12)) * 1e6 * v["launches"]
+            d = detail.setdefault(name, {"launches": 0, "us": 0.0, "target_us": 0.0})
+            d["launches"] += v["launches"]; d["us"] += v["us"]; d["target_us"] += target_us
             entry = kinds.setdefault(KERNEL_KIND.get(name, name), {"launches": 0, "us": 0.0, "target_us": 0.0, "kernels": set()})
             entry["launches"] += v["launches"]; entry["us"] += v["us"]; entry["target_us"] += target_us; entry["kernels"].add(name)
         total = sum(e["us"] for e in kinds.values())
@@ -542,6 +551,9 @@ def design_kernels(model, batch: int, context: int, prompt: int, seed: int, hbm_
                              "frac_of_roofline": round(e["target_us"] / e["us"], 4) if e["us"] > 0 else None, "kernels": sorted(e["kernels"])}
                       for kind, e in sorted(kinds.items(), key=lambda kv: -kv[1]["us"])}
         out[phase + "_sum_us"] = round(total, 1)
+        out[phase + "_by_kernel"] = {name: {"launches": d["launches"], "us_per_launch": round(d["us"] / d["launches"], 2),
+                                            "frac_of_roofline": round(d["target_us"] / d["us"], 4) if d["us"] > 0 else None}
+                                     for name, d in sorted(detail.items(), key=lambda kv: -kv[1]["us"])}
         del stepper
         torch.cuda.empty_cache()
     return out

@@ -685,14 +685,16 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     __syncthreads();
     STAMP(1);
 
-    // Tile t into this warp's stage: lane b fetches box b (K or V, 64-column half, run of box_rows keys).
+    // Tile t into this warp's stage: lane b fetches box b (K or V, 64-column half, run of box_rows keys).  Where keys
+    // and values are one and the same cache (a latent row that serves as both), a tile is fetched once and read as both.
+    const bool one_plane = k_cache == v_cache;
     const int box_rows = min(page_size, TK), boxes = TK / box_rows;
     auto fetch = [&](int t, int slot) {
         unsigned char* stage = ring + (size_t)(warp * STAGES + slot) * TMA_TILE_BYTES;
         uint64_t* bar = full + warp * STAGES + slot;
-        if (lane == 0) mbar_expect_tx(bar, (uint32_t)TMA_TILE_BYTES);
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)(one_plane ? TMA_TILE_BYTES / 2 : TMA_TILE_BYTES));
         __syncwarp();
-        for (int b = lane; b < 2 * NSUB * boxes; b += 32) {
+        for (int b = lane; b < (one_plane ? 1 : 2) * NSUB * boxes; b += 32) {
             const int i = b % boxes, sub = (b / boxes) % NSUB, is_v = b / (boxes * NSUB);
             const int kpos = base + t * TK + i * box_rows;
             const int page = kpos < hi ? pages[kpos / page_size - first_page] : -1;
@@ -744,7 +746,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         unsigned char* stage = ring + (size_t)(warp * STAGES + slot) * TMA_TILE_BYTES;
         uint64_t* bar = full + warp * STAGES + slot;
         const unsigned char* Ks = stage;
-        unsigned char* Vs = stage + NSUB * SUB_BYTES;
+        unsigned char* Vs = one_plane ? stage : stage + NSUB * SUB_BYTES;
         if (!__all_sync(0xffffffffu, mbar_wait(bar, parity))) {      // the lanes agree on whether the wait ran out
             if (lane == 0) { atomicExch(error, 3); *failed = 1; }
             mbar_wait(bar, parity);      // one more bounded chance for the copy to land before the stage is given up

@@ -159,3 +159,87 @@ CISR_EXPORT int cisr_latent_gate(const float* values, const float* gate, int gat
     return launch_kernel(latent_gate_kernel<float>, grid, dim3(256), 0, s, g_pdl, values, gate, gate_stride, gate_col, (float*)out,
                          width, total);
 }
+
+// ---------------------------------------------------------------- few tokens: the per-head products as row kernels
+// With a handful of tokens (decode steps) the two products per head are too small for a library call each: a CTA per
+// (token, head) reads its head's matrix straight from L2.
+//
+// latent_absorb: the work of latent_query and of the product with W_kup in one launch.
+//   q_rows[t, h, r]              = sum_d round(q[t, h, d]) * W_kup[h][d][r]     r < kv_rank, d < plain_dim
+//   q_rows[t, h, kv_rank + ..]   = rotated part, then zeros
+// (the plain part is rounded to the storage type first, as the operand of the library product is).
+template <typename CT>
+__global__ void latent_absorb_kernel(const float* __restrict__ q, int row_stride, int q_col, int heads, int plain_dim,
+                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_half, int interleaved,
+                                     const CT* __restrict__ k_up, CT* __restrict__ q_rows, int kv_rank, int row_width) {
+    extern __shared__ float plain[];            // plain_dim floats
+    pdl_trigger();
+    const int t = blockIdx.x, h = blockIdx.y, rot = 2 * rot_half;
+    const CT* w = k_up + (size_t)h * plain_dim * kv_rank;
+    pdl_wait();
+    const float* row = q + (size_t)t * row_stride + q_col + (size_t)h * (plain_dim + rot);
+    for (int d = threadIdx.x; d < plain_dim; d += blockDim.x) plain[d] = to_float(from_float<CT>(row[d]));
+    __syncthreads();
+    CT* dst = q_rows + ((size_t)t * heads + h) * row_width;
+    for (int r = threadIdx.x; r < row_width; r += blockDim.x) {
+        float acc = 0.f;
+        if (r < kv_rank) {
+#pragma unroll 4
+            for (int d = 0; d < plain_dim; ++d) acc += plain[d] * to_float(w[(size_t)d * kv_rank + r]);
+        } else if (r < kv_rank + rot) {
+            acc = rotated(row + plain_dim, r - kv_rank, rot_half, interleaved, cos_t + (size_t)t * rot_half, sin_t + (size_t)t * rot_half);
+        }
+        dst[r] = from_float<CT>(acc);
+    }
+}
+
+CISR_EXPORT int cisr_latent_absorb(const float* q, int row_stride, int q_col, int heads, int plain_dim, const float* cos_t,
+                                   const float* sin_t, int rot_half, int interleaved, const void* k_up, void* q_rows, int kv_rank,
+                                   int row_width, int dtype, int tokens, void* stream) {
+    if (tokens <= 0) return 0;
+    if (kv_rank + 2 * rot_half > row_width) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(tokens, heads);
+    const size_t smem = sizeof(float) * (size_t)plain_dim;
+    if (dtype == CISR_BF16)
+        return launch_kernel(latent_absorb_kernel<__nv_bfloat16>, grid, dim3(128), smem, s, g_pdl, q, row_stride, q_col, heads, plain_dim,
+                             cos_t, sin_t, rot_half, interleaved, (const __nv_bfloat16*)k_up, (__nv_bfloat16*)q_rows, kv_rank, row_width);
+    return launch_kernel(latent_absorb_kernel<float>, grid, dim3(128), smem, s, g_pdl, q, row_stride, q_col, heads, plain_dim, cos_t,
+                         sin_t, rot_half, interleaved, (const float*)k_up, (float*)q_rows, kv_rank, row_width);
+}
+
+// latent_values: the product with W_vup and the output gate in one launch.
+//   out[t, h * value_dim + j] = (sum_r mixed[t, h, r] * W_vup[h][j][r]) * sigmoid(gate[t, gate_col + h * value_dim + j])
+// mixed [tokens, heads, row_width] is the attention's weighted sum of cache rows (its first kv_rank columns count);
+// gate null: no gate.  A warp per output feature, its lanes striding over the latent.
+template <typename CT>
+__global__ void latent_values_kernel(const CT* __restrict__ mixed, int heads, int row_width, int kv_rank, const CT* __restrict__ v_up,
+                                     int value_dim, const float* __restrict__ gate, int gate_stride, int gate_col, CT* __restrict__ out) {
+    pdl_trigger();
+    const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const CT* w = v_up + (size_t)h * value_dim * kv_rank;
+    pdl_wait();
+    const CT* m = mixed + ((size_t)t * heads + h) * row_width;
+    for (int j = warp; j < value_dim; j += n_warps) {
+        float acc = 0.f;
+        for (int r = lane; r < kv_rank; r += 32) acc += to_float(m[r]) * to_float(w[(size_t)j * kv_rank + r]);
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            const int col = h * value_dim + j;
+            if (gate) acc *= 1.f / (1.f + expf(-gate[(size_t)t * gate_stride + gate_col + col]));
+            out[(size_t)t * heads * value_dim + col] = from_float<CT>(acc);
+        }
+    }
+}
+
+CISR_EXPORT int cisr_latent_values(const void* mixed, int heads, int row_width, int kv_rank, const void* v_up, int value_dim,
+                                   const float* gate, int gate_stride, int gate_col, void* out, int dtype, int tokens, void* stream) {
+    if (tokens <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(tokens, heads);
+    if (dtype == CISR_BF16)
+        return launch_kernel(latent_values_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, g_pdl, (const __nv_bfloat16*)mixed, heads, row_width,
+                             kv_rank, (const __nv_bfloat16*)v_up, value_dim, gate, gate_stride, gate_col, (__nv_bfloat16*)out);
+    return launch_kernel(latent_values_kernel<float>, grid, dim3(256), 0, s, g_pdl, (const float*)mixed, heads, row_width, kv_rank,
+                         (const float*)v_up, value_dim, gate, gate_stride, gate_col, (float*)out);
+}

@@ -450,7 +450,7 @@ def _latent():
     lib = _latent_state.get("lib")
     if lib is None:
         lib = load_library("latent.cu")
-        for name in ("cisr_latent_rows", "cisr_latent_query", "cisr_latent_gate"):
+        for name in ("cisr_latent_rows", "cisr_latent_query", "cisr_latent_gate", "cisr_latent_absorb", "cisr_latent_values"):
             getattr(lib, name).restype = ctypes.c_int
         lib.cisr_latent_set_pdl(int(_pdl_state["on"]))
         _latent_state["lib"] = lib
@@ -524,6 +524,43 @@ def latent_gate(values: torch.Tensor, gate: Optional[torch.Tensor], gate_col: in
             raise KernelError("latent_gate: the gate's columns lie outside its rows")
     _check(_latent().cisr_latent_gate(_p(values), _p(gate), gate.shape[1] if gate is not None else 0, gate_col, _p(out),
                                       dtype_code(out.dtype), tokens, width, _stream()), "latent_gate")
+    return out
+
+
+LATENT_ROW_KERNEL_MAX_TOKENS = 16     # up to here the per-head products run as row kernels, beyond as library products
+
+
+def latent_absorb(q: torch.Tensor, q_col: int, heads: int, plain_dim: int, cos: torch.Tensor, sin: torch.Tensor, rot_half: int,
+                  interleaved: bool, k_up: torch.Tensor, q_rows: torch.Tensor, kv_rank: int) -> torch.Tensor:
+    """Few tokens: `latent_query` and the per-head product with k_up ([heads, plain_dim, kv_rank]) in one launch:
+    q_rows[t, h] = [k_up[h]^T q_plain[t, h] | rotated part | 0]."""
+    _need(q, torch.float32, "q", 2); _need(q_rows, None, "q_rows", 3); _need(k_up, q_rows.dtype, "k_up", 3)
+    _need(cos, torch.float32, "cos", 2); _need(sin, torch.float32, "sin", 2)
+    tokens = q.shape[0]
+    if (k_up.shape != (heads, plain_dim, kv_rank) or q_rows.shape[:2] != (tokens, heads)
+            or q_col + heads * (plain_dim + 2 * rot_half) > q.shape[1] or cos.shape != (tokens, rot_half)):
+        raise KernelError("latent_absorb: shapes disagree")
+    _check(_latent().cisr_latent_absorb(_p(q), q.shape[1], q_col, heads, plain_dim, _p(cos), _p(sin), rot_half, int(interleaved),
+                                        _p(k_up), _p(q_rows), kv_rank, q_rows.shape[2], dtype_code(q_rows.dtype), tokens, _stream()),
+           "latent_absorb")
+    return q_rows
+
+
+def latent_values(mixed: torch.Tensor, v_up: torch.Tensor, gate: Optional[torch.Tensor], gate_col: int, out: torch.Tensor) -> torch.Tensor:
+    """Few tokens: the per-head product with v_up ([heads, value_dim, kv_rank]) over the first kv_rank columns of
+    mixed [tokens, heads, row width], times sigmoid(gate[:, gate_col + ...]) when a gate is given, rounded to out's type."""
+    _need(mixed, None, "mixed", 3); _need(v_up, mixed.dtype, "v_up", 3); _need(out, mixed.dtype, "out", 2)
+    tokens, heads, row_width = mixed.shape
+    _, value_dim, kv_rank = v_up.shape
+    if v_up.shape[0] != heads or kv_rank > row_width or out.shape != (tokens, heads * value_dim):
+        raise KernelError("latent_values: shapes disagree")
+    if gate is not None:
+        _need(gate, torch.float32, "gate", 2)
+        if gate.shape[0] != tokens or gate_col + heads * value_dim > gate.shape[1]:
+            raise KernelError("latent_values: the gate's columns lie outside its rows")
+    _check(_latent().cisr_latent_values(_p(mixed), heads, row_width, kv_rank, _p(v_up), value_dim, _p(gate),
+                                        gate.shape[1] if gate is not None else 0, gate_col, _p(out), dtype_code(out.dtype), tokens,
+                                        _stream()), "latent_values")
     return out
 
 
@@ -1089,6 +1126,9 @@ _DESCRIBE = {
     "latent_rows": lambda proj, *a, **kw: (int(proj.shape[0]), int(proj.shape[1])),
     "latent_query": lambda q, *a, **kw: (int(q.shape[0]), int(q.shape[1])),
     "latent_gate": lambda values, *a, **kw: (int(values.shape[0]), int(values.shape[1])),
+    "latent_absorb": lambda q, q_col, heads, plain_dim, cos, sin, rot_half, interleaved, k_up, q_rows, kv_rank:
+        (int(q.shape[0]), int(heads), int(plain_dim), int(kv_rank)),
+    "latent_values": lambda mixed, v_up, *a, **kw: (int(mixed.shape[0]), int(v_up.shape[0]), int(v_up.shape[1]), int(v_up.shape[2])),
     "moe_router": lambda h, w, *a, **kw: (int(h.shape[0]), int(w.shape[0]), int(w.shape[1])),
     "moe_rows": lambda h, w_up, w_down, chosen, *a, **kw: (int(h.shape[0]), int(w_up.shape[0]), int(w_up.shape[1]), int(w_up.shape[2]), int(chosen.shape[1])),
     "moe_sort": lambda chosen, experts, *a: (int(chosen.shape[0]), int(chosen.shape[1]), int(experts)),

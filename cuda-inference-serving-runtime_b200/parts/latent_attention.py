@@ -128,11 +128,19 @@ class LatentAttention(Mixer):
                             cache=cache.k if cache.write else None, token_req=ctx.token_req, positions=ctx.positions,
                             req_slot=ctx.req_slot, block_table=cache.block_table, page_size=cache.page_size, **table)
         q = linear(cq, self.q_up) if self.q_rank else proj                     # heads of [plain | rotated part] from column 0
-        q_plain = torch.empty((tokens, H, self.plain), dtype=self.dtype, device=device)
         q_rows = torch.empty((tokens, H, self.row), dtype=self.dtype, device=device)
-        kernels.latent_query(q, 0, H, self.plain, plain_out=q_plain, q_rows=q_rows, kv_rank=self.kv_rank, **table)
-        kernels.gemm_heads(q_plain, self.k_up, q_rows, w_is_nk=False)          # q_rows[:, h, :kv_rank] = W_kup_h^T q_plain_h
+        few = tokens <= kernels.LATENT_ROW_KERNEL_MAX_TOKENS
+        if few:      # a decode step: rotation and the product with W_kup_h in one row kernel
+            kernels.latent_absorb(q, 0, H, self.plain, k_up=self.k_up, q_rows=q_rows, kv_rank=self.kv_rank, **table)
+        else:
+            q_plain = torch.empty((tokens, H, self.plain), dtype=self.dtype, device=device)
+            kernels.latent_query(q, 0, H, self.plain, plain_out=q_plain, q_rows=q_rows, kv_rank=self.kv_rank, **table)
+            kernels.gemm_heads(q_plain, self.k_up, q_rows, w_is_nk=False)      # q_rows[:, h, :kv_rank] = W_kup_h^T q_plain_h
         mixed = paged_attention(ctx.plan_for(self), q_rows, cache.k, cache.k, cache, ctx, H, 1, self.scale, None)
+        if few:      # W_vup_h (weighted sum of latents), gate and rounding in one row kernel
+            values = kernels.latent_values(mixed, self.v_up, proj if self.gate else None, self.gate_col,
+                                           torch.empty((tokens, H * self.vdim), dtype=self.dtype, device=device))
+            return linear(values, self.o)
         values = torch.empty((tokens, H, self.vdim), dtype=torch.float32, device=device)
         kernels.gemm_heads(mixed, self.v_up, values, w_is_nk=True)             # W_vup_h (weighted sum of latents)
         values = values.view(tokens, H * self.vdim)
