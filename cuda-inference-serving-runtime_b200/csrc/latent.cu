@@ -168,11 +168,14 @@ CISR_EXPORT int cisr_latent_gate(const float* values, const float* gate, int gat
 //   q_rows[t, h, r]              = sum_d round(q[t, h, d]) * W_kup[h][d][r]     r < kv_rank, d < plain_dim
 //   q_rows[t, h, kv_rank + ..]   = rotated part, then zeros
 // (the plain part is rounded to the storage type first, as the operand of the library product is).
+constexpr int ABSORB_SPLIT = 4;       // the sum over a head's plain coordinates is cut into this many parts, each with its loads in flight at once
 template <typename CT>
 __global__ void latent_absorb_kernel(const float* __restrict__ q, int row_stride, int q_col, int heads, int plain_dim,
                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_half, int interleaved,
                                      const CT* __restrict__ k_up, CT* __restrict__ q_rows, int kv_rank, int row_width) {
-    extern __shared__ float plain[];            // plain_dim floats
+    extern __shared__ float absorb_smem[];      // plain_dim floats, then ABSORB_SPLIT * kv_rank partial sums
+    float* plain = absorb_smem;
+    float* part = absorb_smem + plain_dim;
     pdl_trigger();
     const int t = blockIdx.x, h = blockIdx.y, rot = 2 * rot_half;
     const CT* w = k_up + (size_t)h * plain_dim * kv_rank;
@@ -180,12 +183,21 @@ __global__ void latent_absorb_kernel(const float* __restrict__ q, int row_stride
     const float* row = q + (size_t)t * row_stride + q_col + (size_t)h * (plain_dim + rot);
     for (int d = threadIdx.x; d < plain_dim; d += blockDim.x) plain[d] = to_float(from_float<CT>(row[d]));
     __syncthreads();
+    const int per = (plain_dim + ABSORB_SPLIT - 1) / ABSORB_SPLIT;
+    for (int i = threadIdx.x; i < ABSORB_SPLIT * kv_rank; i += blockDim.x) {
+        const int g = i / kv_rank, r = i - g * kv_rank, d0 = g * per, d1 = min(plain_dim, d0 + per);
+        float acc = 0.f;
+#pragma unroll 8
+        for (int d = d0; d < d1; ++d) acc += plain[d] * to_float(w[(size_t)d * kv_rank + r]);
+        part[i] = acc;
+    }
+    __syncthreads();
     CT* dst = q_rows + ((size_t)t * heads + h) * row_width;
     for (int r = threadIdx.x; r < row_width; r += blockDim.x) {
         float acc = 0.f;
         if (r < kv_rank) {
-#pragma unroll 4
-            for (int d = 0; d < plain_dim; ++d) acc += plain[d] * to_float(w[(size_t)d * kv_rank + r]);
+#pragma unroll
+            for (int g = 0; g < ABSORB_SPLIT; ++g) acc += part[g * kv_rank + r];       // the parts in their fixed order
         } else if (r < kv_rank + rot) {
             acc = rotated(row + plain_dim, r - kv_rank, rot_half, interleaved, cos_t + (size_t)t * rot_half, sin_t + (size_t)t * rot_half);
         }
@@ -200,11 +212,13 @@ CISR_EXPORT int cisr_latent_absorb(const float* q, int row_stride, int q_col, in
     if (kv_rank + 2 * rot_half > row_width) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(tokens, heads);
-    const size_t smem = sizeof(float) * (size_t)plain_dim;
+    const size_t smem = sizeof(float) * ((size_t)plain_dim + (size_t)ABSORB_SPLIT * kv_rank);
+    if (smem > 48 * 1024) return -3;
+    const int threads = ABSORB_SPLIT * kv_rank >= 512 ? 512 : (ABSORB_SPLIT * kv_rank >= 256 ? 256 : 128);
     if (dtype == CISR_BF16)
-        return launch_kernel(latent_absorb_kernel<__nv_bfloat16>, grid, dim3(128), smem, s, g_pdl, q, row_stride, q_col, heads, plain_dim,
+        return launch_kernel(latent_absorb_kernel<__nv_bfloat16>, grid, dim3(threads), smem, s, g_pdl, q, row_stride, q_col, heads, plain_dim,
                              cos_t, sin_t, rot_half, interleaved, (const __nv_bfloat16*)k_up, (__nv_bfloat16*)q_rows, kv_rank, row_width);
-    return launch_kernel(latent_absorb_kernel<float>, grid, dim3(128), smem, s, g_pdl, q, row_stride, q_col, heads, plain_dim, cos_t,
+    return launch_kernel(latent_absorb_kernel<float>, grid, dim3(threads), smem, s, g_pdl, q, row_stride, q_col, heads, plain_dim, cos_t,
                          sin_t, rot_half, interleaved, (const float*)k_up, (float*)q_rows, kv_rank, row_width);
 }
 
@@ -216,11 +230,12 @@ template <typename CT>
 __global__ void latent_values_kernel(const CT* __restrict__ mixed, int heads, int row_width, int kv_rank, const CT* __restrict__ v_up,
                                      int value_dim, const float* __restrict__ gate, int gate_stride, int gate_col, CT* __restrict__ out) {
     pdl_trigger();
-    const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const int warp = blockIdx.z * n_warps + (threadIdx.x >> 5), all_warps = gridDim.z * n_warps;    // a warp has one feature when the grid is large enough
     const CT* w = v_up + (size_t)h * value_dim * kv_rank;
     pdl_wait();
     const CT* m = mixed + ((size_t)t * heads + h) * row_width;
-    for (int j = warp; j < value_dim; j += n_warps) {
+    for (int j = warp; j < value_dim; j += all_warps) {
         float acc = 0.f;
         for (int r = lane; r < kv_rank; r += 32) acc += to_float(m[r]) * to_float(w[(size_t)j * kv_rank + r]);
         acc = warp_sum(acc);
@@ -236,7 +251,7 @@ CISR_EXPORT int cisr_latent_values(const void* mixed, int heads, int row_width, 
                                    const float* gate, int gate_stride, int gate_col, void* out, int dtype, int tokens, void* stream) {
     if (tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(tokens, heads);
+    const dim3 grid(tokens, heads, (value_dim + 7) / 8);
     if (dtype == CISR_BF16)
         return launch_kernel(latent_values_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, g_pdl, (const __nv_bfloat16*)mixed, heads, row_width,
                              kv_rank, (const __nv_bfloat16*)v_up, value_dim, gate, gate_stride, gate_col, (__nv_bfloat16*)out);

@@ -118,10 +118,11 @@ CISR_EXPORT int cisr_moe_router(const void* h, const void* w, int dtype, int tok
     const size_t smem = (size_t)(2 * n_experts + (n_groups > 0 ? n_groups : 0)) * sizeof(float);
     if (smem > 48 * 1024) return -3;
     cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 32 * (n_experts >= 16 ? 16 : (n_experts >= 8 ? 8 : 4));     // a warp per expert where there are that many
     if (dtype == CISR_BF16)
-        return launch_kernel(moe_router_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), smem, s, g_pdl, (const __nv_bfloat16*)h,
+        return launch_kernel(moe_router_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, s, g_pdl, (const __nv_bfloat16*)h,
                              (const __nv_bfloat16*)w, hidden, n_experts, top, n_groups, keep, route_scale, chosen, weight);
-    return launch_kernel(moe_router_kernel<float>, dim3(tokens), dim3(128), smem, s, g_pdl, (const float*)h, (const float*)w, hidden,
+    return launch_kernel(moe_router_kernel<float>, dim3(tokens), dim3(threads), smem, s, g_pdl, (const float*)h, (const float*)w, hidden,
                          n_experts, top, n_groups, keep, route_scale, chosen, weight);
 }
 
