@@ -453,7 +453,7 @@ KERNEL_KIND = {   # which kernels of the two designs are alike
     "moe_rows": "feed-forward product, few tokens", "gemm_heads": "product per head", "attn_prefill_wide": "prompt attention", "attn_prefill": "prompt attention",
     "attn_decode": "decode attention", "merge_out_proj": "product, few tokens", "add_rmsnorm": "norm", "embedding": "row kernels", "rope_store": "row kernels",
     "latent_rows": "row kernels", "latent_query": "row kernels", "latent_gate": "row kernels", "latent_absorb": "product per head",
-    "latent_values": "product per head", "moe_router": "row kernels", "moe_gather": "row kernels",
+    "latent_values": "product per head", "moe_select": "row kernels", "moe_gather": "row kernels",
     "moe_combine": "row kernels", "moe_sort": "bookkeeping", "stream_add": "row kernels", "swiglu": "row kernels"}
 
 
@@ -503,9 +503,8 @@ def generic_need(name: str, shape: tuple, cache_tokens: int, causal: int):
     if name == "moe_combine":
         tokens, top, hidden = shape
         return tokens * hidden * 4 * (top + 1), 0.0
-    if name == "moe_router":
-        tokens, experts, hidden = shape
-        return (tokens + experts) * hidden * 2, 2.0 * tokens * experts * hidden
+    if name == "moe_select":
+        return shape[0] * shape[1] * 4, 0.0
     return 0, 0.0
 
 

@@ -1,7 +1,7 @@
 // Routed experts: a router that scores every expert per token, picks a few, and the chosen experts' small
 // feed-forward layers, summed with the router's weights.
 //
-//   scores s = sigmoid(W_router h)                       (float arithmetic whatever the storage type)
+//   scores s = sigmoid(W_router h)                       (float sums and float arithmetic whatever the storage type)
 //   experts form n_groups equal groups of neighbours; a group's score is the sum of its two best members; only members
 //   of the `keep` best groups can be chosen (n_groups 0: all can)
 //   the `top` best open experts are chosen, weight = s * route_scale (not renormalised)
@@ -53,28 +53,32 @@ __device__ __forceinline__ float warp_dot(const __nv_bfloat16* __restrict__ a, c
     return warp_sum(acc);
 }
 
-// ---------------------------------------------------------------- router
-// One CTA per token.  Shared memory: n_experts scores, n_experts flags, n_groups group scores.
-template <typename T>
-__global__ void moe_router_kernel(const T* __restrict__ h, const T* __restrict__ w, int hidden, int n_experts, int top,
-                                  int n_groups, int keep, float route_scale, int* __restrict__ chosen,
-                                  float* __restrict__ weight) {
-    extern __shared__ float smem[];
-    float* score = smem;
-    int* open_ = reinterpret_cast<int*>(smem + n_experts);
-    float* group_score = smem + 2 * n_experts;
+// ---------------------------------------------------------------- router: from logits to the chosen experts
+// The logits z = W_router h come from the engine's matrix products (float sums of bfloat16 or float operands).  A warp
+// per token: its lanes turn the logits into scores and score the groups, lane 0 then keeps the best groups and takes
+// the best open experts one after the other (ties go to the lower index).  Shared memory per warp: n_experts scores,
+// n_experts flags, n_groups group scores.
+constexpr int SELECT_WARPS = 4;
+__global__ void __launch_bounds__(32 * SELECT_WARPS)
+moe_select_kernel(const float* __restrict__ logits, int tokens, int n_experts, int top, int n_groups, int keep, float route_scale,
+                  int* __restrict__ chosen, float* __restrict__ weight) {
+    extern __shared__ float select_smem[];
     pdl_trigger();
     pdl_wait();
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    const T* row = h + (size_t)t * hidden;
-    for (int e = warp; e < n_experts; e += n_warps) {
-        const float z = warp_dot(w + (size_t)e * hidden, row, hidden, lane);
-        if (lane == 0) score[e] = 1.f / (1.f + expf(-z));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, t = blockIdx.x * SELECT_WARPS + warp;
+    if (t >= tokens) return;
+    const int per_warp = 2 * n_experts + n_groups;
+    float* score = select_smem + (size_t)warp * per_warp;
+    int* open_ = reinterpret_cast<int*>(score + n_experts);
+    float* group_score = score + 2 * n_experts;
+    for (int e = lane; e < n_experts; e += 32) {
+        score[e] = 1.f / (1.f + expf(-logits[(size_t)t * n_experts + e]));
+        open_[e] = n_groups > 0 ? 0 : 1;
     }
-    __syncthreads();
+    __syncwarp();
     if (n_groups > 0) {
         const int per = n_experts / n_groups;
-        for (int g = threadIdx.x; g < n_groups; g += blockDim.x) {
+        for (int g = lane; g < n_groups; g += 32) {
             float best = -1.f, second = -1.f;
             for (int i = 0; i < per; ++i) {
                 const float s = score[g * per + i];
@@ -83,13 +87,12 @@ __global__ void moe_router_kernel(const T* __restrict__ h, const T* __restrict__
             }
             group_score[g] = per > 1 ? best + second : best;
         }
+        __syncwarp();
     }
-    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) open_[e] = n_groups > 0 ? 0 : 1;
-    __syncthreads();
-    if (threadIdx.x == 0) {
+    if (lane == 0) {
         if (n_groups > 0) {
             const int per = n_experts / n_groups;
-            for (int k = 0; k < keep; ++k) {          // the best groups, one after the other; ties go to the lower index
+            for (int k = 0; k < keep; ++k) {
                 int best = -1;
                 for (int g = 0; g < n_groups; ++g)
                     if (group_score[g] >= 0.f && (best < 0 || group_score[g] > group_score[best])) best = g;
@@ -110,20 +113,16 @@ __global__ void moe_router_kernel(const T* __restrict__ h, const T* __restrict__
     }
 }
 
-CISR_EXPORT int cisr_moe_router(const void* h, const void* w, int dtype, int tokens, int hidden, int n_experts, int top,
-                                int n_groups, int keep, float route_scale, int* chosen, float* weight, void* stream) {
+CISR_EXPORT int cisr_moe_select(const float* logits, int tokens, int n_experts, int top, int n_groups, int keep, float route_scale,
+                                int* chosen, float* weight, void* stream) {
     if (tokens <= 0) return 0;
     if (n_experts <= 0 || top <= 0 || top > n_experts || (n_groups > 0 && (n_experts % n_groups || keep <= 0 || keep > n_groups)))
         return -2;
-    const size_t smem = (size_t)(2 * n_experts + (n_groups > 0 ? n_groups : 0)) * sizeof(float);
+    const size_t smem = (size_t)SELECT_WARPS * (2 * n_experts + (n_groups > 0 ? n_groups : 0)) * sizeof(float);
     if (smem > 48 * 1024) return -3;
-    cudaStream_t s = (cudaStream_t)stream;
-    const int threads = 32 * (n_experts >= 16 ? 16 : (n_experts >= 8 ? 8 : 4));     // a warp per expert where there are that many
-    if (dtype == CISR_BF16)
-        return launch_kernel(moe_router_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, s, g_pdl, (const __nv_bfloat16*)h,
-                             (const __nv_bfloat16*)w, hidden, n_experts, top, n_groups, keep, route_scale, chosen, weight);
-    return launch_kernel(moe_router_kernel<float>, dim3(tokens), dim3(threads), smem, s, g_pdl, (const float*)h, (const float*)w, hidden,
-                         n_experts, top, n_groups, keep, route_scale, chosen, weight);
+    return launch_kernel(moe_select_kernel, dim3((tokens + SELECT_WARPS - 1) / SELECT_WARPS), dim3(32 * SELECT_WARPS), smem,
+                         (cudaStream_t)stream, g_pdl, logits, tokens, n_experts, top, n_groups > 0 ? n_groups : 0, keep, route_scale, chosen,
+                         weight);
 }
 
 // ---------------------------------------------------------------- few tokens: a warp per output feature

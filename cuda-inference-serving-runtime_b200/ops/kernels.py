@@ -572,7 +572,7 @@ def _moe():
     lib = _moe_state.get("lib")
     if lib is None:
         lib = load_library("moe.cu")
-        for name in ("cisr_moe_router", "cisr_moe_rows", "cisr_moe_sort", "cisr_moe_gather", "cisr_moe_combine"):
+        for name in ("cisr_moe_select", "cisr_moe_rows", "cisr_moe_sort", "cisr_moe_gather", "cisr_moe_combine"):
             getattr(lib, name).restype = ctypes.c_int
         lib.cisr_moe_set_pdl(int(_pdl_state["on"]))
         _moe_state["lib"] = lib
@@ -583,16 +583,16 @@ def moe_jobs():
     return [("moe.cu", {}, ())]
 
 
-def moe_router(h: torch.Tensor, w: torch.Tensor, top: int, n_groups: int, keep: int, route_scale: float,
-               chosen: torch.Tensor, weight: torch.Tensor) -> None:
-    """Per token: sigmoid scores of every expert (float arithmetic), the open groups, the `top` chosen experts
-    (`chosen`, int32 [tokens, top], best first) and their weights score * route_scale (`weight`, float)."""
-    _need(h, None, "h", 2); _need(w, h.dtype, "w", 2); _need(chosen, torch.int32, "chosen", 2); _need(weight, torch.float32, "weight", 2)
-    tokens, hidden = h.shape
-    if w.shape[1] != hidden or chosen.shape != (tokens, top) or weight.shape != (tokens, top):
-        raise KernelError("moe_router: shapes disagree")
-    _check(_moe().cisr_moe_router(_p(h), _p(w), dtype_code(h.dtype), tokens, hidden, w.shape[0], top, n_groups, keep,
-                                  ctypes.c_float(route_scale), _p(chosen), _p(weight), _stream()), "moe_router")
+def moe_select(logits: torch.Tensor, top: int, n_groups: int, keep: int, route_scale: float, chosen: torch.Tensor,
+               weight: torch.Tensor) -> None:
+    """Per token, from the router's logits (float [tokens, experts]): sigmoid scores, the open groups, the `top` chosen
+    experts (`chosen`, int32 [tokens, top], best first) and their weights score * route_scale (`weight`, float)."""
+    _need(logits, torch.float32, "logits", 2); _need(chosen, torch.int32, "chosen", 2); _need(weight, torch.float32, "weight", 2)
+    tokens, experts = logits.shape
+    if chosen.shape != (tokens, top) or weight.shape != (tokens, top):
+        raise KernelError("moe_select: shapes disagree")
+    _check(_moe().cisr_moe_select(_p(logits), tokens, experts, top, n_groups, keep, ctypes.c_float(route_scale), _p(chosen),
+                                  _p(weight), _stream()), "moe_select")
 
 
 def moe_rows(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
@@ -682,8 +682,8 @@ def moe_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chose
     tile_group = torch.empty(rows // MOE_TILE, dtype=torch.int32, device=device)
     moe_sort(chosen, experts, row_of, src_token, tile_group)
     sorted_h = moe_gather(h, src_token, torch.empty((rows, hidden), dtype=torch.bfloat16, device=device))
-    act = gemm_tcgen05_grouped(sorted_h, w_up, torch.empty((rows, ff), dtype=torch.bfloat16, device=device), tile_group)
-    sorted_out = gemm_tcgen05_grouped(act, w_down, torch.empty((rows, hidden), dtype=torch.float32, device=device), tile_group)
+    act = gemm_tcgen05_grouped(sorted_h, w_up, torch.empty((rows, ff), dtype=torch.bfloat16, device=device), tile_group, tokens * top)
+    sorted_out = gemm_tcgen05_grouped(act, w_down, torch.empty((rows, hidden), dtype=torch.float32, device=device), tile_group, tokens * top)
     return moe_combine(sorted_out, row_of, weight, out)
 
 
@@ -1017,10 +1017,11 @@ def gemm_tcgen05_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> 
     return out
 
 
-def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor) -> torch.Tensor:
+def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor,
+                         rows_in_use: Optional[int] = None) -> torch.Tensor:
     """Rows of `a` (bfloat16 [M, K], M a multiple of 128) sorted by group, each 128-row tile with its group's matrix
     w[g] (w bfloat16 [groups, N, K]; tile_group int32 [M / 128], -1: skip the tile).  out float [M, N]: the products;
-    out bfloat16 [M, N]: max(product, 0)^2."""
+    out bfloat16 [M, N]: max(product, 0)^2.  `rows_in_use` (how many rows are not padding) only labels measurements."""
     _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 3); _need(out, None, "out", 2); _need(tile_group, torch.int32, "tile_group", 1)
     m, k = a.shape
     groups, n, _ = w.shape
@@ -1129,12 +1130,13 @@ _DESCRIBE = {
     "latent_absorb": lambda q, q_col, heads, plain_dim, cos, sin, rot_half, interleaved, k_up, q_rows, kv_rank:
         (int(q.shape[0]), int(heads), int(plain_dim), int(kv_rank)),
     "latent_values": lambda mixed, v_up, *a, **kw: (int(mixed.shape[0]), int(v_up.shape[0]), int(v_up.shape[1]), int(v_up.shape[2])),
-    "moe_router": lambda h, w, *a, **kw: (int(h.shape[0]), int(w.shape[0]), int(w.shape[1])),
+    "moe_select": lambda logits, *a, **kw: (int(logits.shape[0]), int(logits.shape[1])),
     "moe_rows": lambda h, w_up, w_down, chosen, *a, **kw: (int(h.shape[0]), int(w_up.shape[0]), int(w_up.shape[1]), int(w_up.shape[2]), int(chosen.shape[1])),
     "moe_sort": lambda chosen, experts, *a: (int(chosen.shape[0]), int(chosen.shape[1]), int(experts)),
     "moe_gather": lambda h, src_token, sorted_h: (int(sorted_h.shape[0]), int(sorted_h.shape[1])),
     "moe_combine": lambda sorted_out, row_of, weight, out: (int(out.shape[0]), int(weight.shape[1]), int(out.shape[1])),
-    "gemm_tcgen05_grouped": lambda a, w, out, tile_group: (int(a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2]), out.dtype == torch.bfloat16),
+    "gemm_tcgen05_grouped": lambda a, w, out, tile_group, rows_in_use=None:
+        (int(rows_in_use or a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2]), out.dtype == torch.bfloat16),
     "gemm_heads": lambda a, w, out, w_is_nk: (int(a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2])),
     "swiglu": lambda gate_up, out: (int(out.shape[0]), int(out.shape[1])),
     "rotary_tables": lambda positions, inv_freq, cos, sin: (int(cos.shape[0]), int(cos.shape[1])),

@@ -1,6 +1,6 @@
 """Routed experts: many small feed-forward layers of which each token uses a few.
 
-    scores    s = sigmoid(W_router h), in float
+    scores    s = sigmoid(W_router h): float sums (one of the engine's matrix products), float sigmoid
     groups    the experts form `groups` equal groups of neighbours; a group's score is the sum of its two best members;
               only members of the `keep` best groups can be chosen (groups 0: every expert can)
     choice    the `top` best open experts, each weighted by s * route_scale (not renormalised)
@@ -18,6 +18,7 @@ import torch
 
 from ..ops import kernels
 from .base import FEED_FORWARDS, FeedForward, TensorNeed, register
+from .linear import linear
 
 ACTIVATIONS = ("relu_squared",)
 DEFAULT_NAMES = {"router": "router.weight", "up": "experts.{}.up.weight", "down": "experts.{}.down.weight"}
@@ -62,14 +63,15 @@ class RoutedExperts(FeedForward):
         self.down = torch.stack([tensors[self.names["down"].format(e)] for e in range(self.experts)]).contiguous()
 
     def kernel_jobs(self):
-        return kernels.moe_jobs() + (kernels.tcgen05_jobs() if self.dtype == torch.bfloat16 else [])
+        return kernels.moe_jobs() + kernels.gemm_jobs(self.dtype) + (kernels.skinny_jobs() if self.dtype == torch.bfloat16 else [])
 
     def route(self, h: torch.Tensor):
         """(chosen experts int32 [tokens, top], best first; their weights float [tokens, top])."""
         tokens = h.shape[0]
         chosen = torch.empty((tokens, self.top), dtype=torch.int32, device=h.device)
         weight = torch.empty((tokens, self.top), dtype=torch.float32, device=h.device)
-        kernels.moe_router(h, self.router, self.top, self.groups, self.keep, self.route_scale, chosen, weight)
+        logits = linear(h, self.router)          # float sums, by the engine's products for this many tokens
+        kernels.moe_select(logits, self.top, self.groups, self.keep, self.route_scale, chosen, weight)
         return chosen, weight
 
     def forward(self, h, ctx):

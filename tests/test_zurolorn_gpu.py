@@ -70,7 +70,9 @@ def stepper_for(model, steps, slack_pages=0):
 @pytest.mark.parametrize("experts, top, groups, keep, hidden", [(8, 2, 4, 2, 128), (6, 1, 0, 0, 72), (9, 2, 3, 1, 40), (16, 4, 8, 3, 192),
                                                                 (4, 4, 2, 2, 64), (12, 3, 12, 5, 96)])
 def test_router_kernel(dtype, experts, top, groups, keep, hidden):
-    from cisr_b200.ops import kernels
+    """The router part alone (logits by the engine's product, choice by the selection kernel), inputs equal to the bit."""
+    from cisr_b200.config import PartSpec
+    from cisr_b200.parts import FEED_FORWARDS, build_part
     g = torch.Generator().manual_seed(experts * 100 + top)
     h = torch.randn(57, hidden, generator=g).to(dtype)
     w = (3.0 / hidden ** 0.5 * torch.randn(experts, hidden, generator=g)).to(dtype)
@@ -78,10 +80,17 @@ def test_router_kernel(dtype, experts, top, groups, keep, hidden):
     if groups:
         router["groups"] = {"count": groups, "keep": keep}
     want_ids, want_w = pz.route(h.to(F), w.to(F), router)
-    chosen = torch.empty((57, top), dtype=torch.int32, device="cuda")
-    weight = torch.empty((57, top), dtype=torch.float32, device="cuda")
-    kernels.moe_router(h.cuda(), w.cuda(), top, groups, keep, 1.75, chosen, weight)
-    assert torch.equal(chosen.cpu().long(), want_ids), "the kernel chose other experts (inputs are equal to the bit, float sums differ in the last place only)"
+    part = build_part(FEED_FORWARDS, PartSpec("routed_experts", {"hidden_size": hidden, "expert_size": 8, "experts": experts, "top": top,
+                                                                 "groups": groups, "keep": keep, "route_scale": 1.75}), dtype, "feed-forward")
+    from cisr_b200.ops import build
+    build.compile_many(part.kernel_jobs())
+    tensors = {"router.weight": w.cuda()}
+    for e in range(experts):
+        tensors[f"experts.{e}.up.weight"] = torch.zeros(8, hidden, dtype=dtype, device="cuda")
+        tensors[f"experts.{e}.down.weight"] = torch.zeros(hidden, 8, dtype=dtype, device="cuda")
+    part.load(tensors)
+    chosen, weight = part.route(h.cuda())
+    assert torch.equal(chosen.cpu().long(), want_ids), "the router chose other experts (inputs are equal to the bit, float sums differ in the last place only)"
     assert torch.allclose(weight.cpu().to(F), want_w, rtol=1e-5, atol=1e-6)
 
 
