@@ -55,8 +55,8 @@ __device__ __forceinline__ float warp_dot(const __nv_bfloat16* __restrict__ a, c
 
 // ---------------------------------------------------------------- router: from logits to the chosen experts
 // The logits z = W_router h come from the engine's matrix products (float sums of bfloat16 or float operands).  A warp
-// per token: its lanes turn the logits into scores and score the groups, lane 0 then keeps the best groups and takes
-// the best open experts one after the other (ties go to the lower index).  Shared memory per warp: n_experts scores,
+// per token: its lanes turn the logits into scores and score the groups, then keep the best groups and take the best
+// open experts one after the other (ties go to the lower index).  Shared memory per warp: n_experts scores,
 // n_experts flags, n_groups group scores.
 constexpr int SELECT_WARPS = 4;
 __global__ void __launch_bounds__(32 * SELECT_WARPS)
@@ -89,27 +89,44 @@ moe_select_kernel(const float* __restrict__ logits, int tokens, int n_experts, i
         }
         __syncwarp();
     }
-    if (lane == 0) {
-        if (n_groups > 0) {
-            const int per = n_experts / n_groups;
-            for (int k = 0; k < keep; ++k) {
-                int best = -1;
-                for (int g = 0; g < n_groups; ++g)
-                    if (group_score[g] >= 0.f && (best < 0 || group_score[g] > group_score[best])) best = g;
-                if (best < 0) break;
-                group_score[best] = -1.f;
-                for (int i = 0; i < per; ++i) open_[best * per + i] = 1;
-            }
+    // The best of the warp's candidates: each lane looks at every 32nd, then the lanes compare (the larger score wins, the
+    // lower index among equals), so every round costs a few shuffles instead of a walk over all experts by one lane.
+    auto warp_best = [&](const float* value, const int* allowed, int n, float& best_value) {
+        float bv = -1.f; int bi = 0x7fffffff;
+        for (int i = lane; i < n; i += 32)
+            if ((!allowed || allowed[i]) && value[i] > bv) { bv = value[i]; bi = i; }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
-        for (int k = 0; k < top; ++k) {
-            int best = -1;
-            for (int e = 0; e < n_experts; ++e)
-                if (open_[e] && (best < 0 || score[e] > score[best])) best = e;
-            if (best < 0) best = 0;                    // fewer open experts than `top`: the host refuses such a configuration
+        best_value = bv;
+        return bi;
+    };
+    if (n_groups > 0) {
+        const int per = n_experts / n_groups;
+        for (int k = 0; k < keep; ++k) {
+            float v;
+            const int best = warp_best(group_score, nullptr, n_groups, v);
+            if (best == 0x7fffffff) break;
+            __syncwarp();
+            if (lane == 0) group_score[best] = -2.f;                 // below every score and below the "nothing found" mark
+            for (int i = lane; i < per; i += 32) open_[best * per + i] = 1;
+            __syncwarp();
+        }
+    }
+    for (int k = 0; k < top; ++k) {
+        float v;
+        int best = warp_best(score, open_, n_experts, v);
+        __syncwarp();
+        if (lane == 0) {
+            if (best == 0x7fffffff) best = 0;                        // fewer open experts than `top`: the host refuses such a configuration
             else open_[best] = 0;
             chosen[(size_t)t * top + k] = best;
             weight[(size_t)t * top + k] = score[best] * route_scale;
         }
+        __syncwarp();
     }
 }
 
@@ -141,12 +158,13 @@ moe_up_rows_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const in
     if (lane == 0) { const float r = fmaxf(z, 0.f); act[(size_t)pair * ff + f] = from_float<T>(r * r); }
 }
 
-// out[t, c] = sum_k weight[t, k] * (W_down[e_k][c] . act[t * top + k]);   W_down [experts, hidden, ff]; experts in the
-// order the router chose them.
+// out[t, c] = out_scale[c] * sum_k weight[t, k] * (W_down[e_k][c] . act[t * top + k]);   W_down [experts, hidden, ff];
+// experts in the order the router chose them; out_scale (a layer scale, one factor per channel) may be null.
 template <typename T>
 __global__ void __launch_bounds__(32 * ROW_WARPS)
 moe_down_rows_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ chosen,
-                     const float* __restrict__ weight, int hidden, int ff, int top, float* __restrict__ out) {
+                     const float* __restrict__ weight, int hidden, int ff, int top, const float* __restrict__ out_scale,
+                     float* __restrict__ out) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x & 31, c = blockIdx.y * ROW_WARPS + (threadIdx.x >> 5);
@@ -156,11 +174,12 @@ moe_down_rows_kernel(const T* __restrict__ act, const T* __restrict__ w_down, co
         const int e = chosen[(size_t)t * top + k];
         acc += weight[(size_t)t * top + k] * warp_dot(w_down + ((size_t)e * hidden + c) * ff, act + ((size_t)t * top + k) * ff, ff, lane);
     }
-    if (lane == 0) out[(size_t)t * hidden + c] = acc;
+    if (lane == 0) out[(size_t)t * hidden + c] = out_scale ? acc * out_scale[c] : acc;
 }
 
 CISR_EXPORT int cisr_moe_rows(const void* h, const void* w_up, const void* w_down, int dtype, const int* chosen,
-                              const float* weight, int tokens, int hidden, int ff, int top, void* act, float* out, void* stream) {
+                              const float* weight, int tokens, int hidden, int ff, int top, void* act, const float* out_scale,
+                              float* out, void* stream) {
     if (tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 up_grid(tokens * top, (ff + ROW_WARPS - 1) / ROW_WARPS), down_grid(tokens, (hidden + ROW_WARPS - 1) / ROW_WARPS);
@@ -170,13 +189,13 @@ CISR_EXPORT int cisr_moe_rows(const void* h, const void* w_up, const void* w_dow
                            (const __nv_bfloat16*)w_up, chosen, hidden, ff, top, (__nv_bfloat16*)act);
         if (st) return st;
         return launch_kernel(moe_down_rows_kernel<__nv_bfloat16>, down_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl,
-                             (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, chosen, weight, hidden, ff, top, out);
+                             (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, chosen, weight, hidden, ff, top, out_scale, out);
     }
     st = launch_kernel(moe_up_rows_kernel<float>, up_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl, (const float*)h, (const float*)w_up,
                        chosen, hidden, ff, top, (float*)act);
     if (st) return st;
     return launch_kernel(moe_down_rows_kernel<float>, down_grid, dim3(32 * ROW_WARPS), 0, s, g_pdl, (const float*)act,
-                         (const float*)w_down, chosen, weight, hidden, ff, top, out);
+                         (const float*)w_down, chosen, weight, hidden, ff, top, out_scale, out);
 }
 
 // ---------------------------------------------------------------- many tokens: rows sorted by expert
@@ -226,16 +245,16 @@ __global__ void moe_gather_kernel(const uint4* __restrict__ h, const int* __rest
         sorted[(size_t)row * row_vec + i] = src >= 0 ? h[(size_t)src * row_vec + i] : make_uint4(0, 0, 0, 0);
 }
 
-// out[t, c] = sum_k weight[t, k] * sorted_out[row_of[t * top + k], c], k in the router's order.
+// out[t, c] = out_scale[c] * sum_k weight[t, k] * sorted_out[row_of[t * top + k], c], k in the router's order (out_scale null: 1).
 __global__ void moe_combine_kernel(const float* __restrict__ sorted_out, const int* __restrict__ row_of, const float* __restrict__ weight,
-                                   int top, int hidden, float* __restrict__ out) {
+                                   int top, int hidden, const float* __restrict__ out_scale, float* __restrict__ out) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; ++k) acc += weight[(size_t)t * top + k] * sorted_out[(size_t)row_of[(size_t)t * top + k] * hidden + c];
-        out[(size_t)t * hidden + c] = acc;
+        out[(size_t)t * hidden + c] = out_scale ? acc * out_scale[c] : acc;
     }
 }
 
@@ -259,8 +278,8 @@ CISR_EXPORT int cisr_moe_gather(const void* h, const int* src_token, void* sorte
 }
 
 CISR_EXPORT int cisr_moe_combine(const float* sorted_out, const int* row_of, const float* weight, int tokens, int top, int hidden,
-                                 float* out, void* stream) {
+                                 const float* out_scale, float* out, void* stream) {
     if (tokens <= 0) return 0;
     return launch_kernel(moe_combine_kernel, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, g_pdl, sorted_out, row_of, weight, top,
-                         hidden, out);
+                         hidden, out_scale, out);
 }

@@ -595,10 +595,18 @@ def moe_select(logits: torch.Tensor, top: int, n_groups: int, keep: int, route_s
                                   _p(weight), _stream()), "moe_select")
 
 
+def _channel_scale(scale: Optional[torch.Tensor], hidden: int, what: str) -> None:
+    if scale is not None:
+        _need(scale, torch.float32, "out_scale", 1)
+        if scale.numel() != hidden:
+            raise KernelError(f"{what}: one output scale per channel is needed")
+
+
 def moe_rows(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
-             act: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+             act: torch.Tensor, out: torch.Tensor, out_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out (float [tokens, hidden]) = sum over a token's chosen experts of weight * W_down_e relu(W_up_e h)^2, a warp per
-    output feature; w_up [experts, ff, hidden], w_down [experts, hidden, ff]; `act` [tokens * top, ff] is scratch."""
+    output feature; w_up [experts, ff, hidden], w_down [experts, hidden, ff]; `act` [tokens * top, ff] is scratch; `out_scale`
+    (float, one per channel) multiplies the sum."""
     _need(h, None, "h", 2); _need(w_up, h.dtype, "w_up", 3); _need(w_down, h.dtype, "w_down", 3); _need(act, h.dtype, "act", 2)
     _need(out, torch.float32, "out", 2); _need(chosen, torch.int32, "chosen", 2); _need(weight, torch.float32, "weight", 2)
     tokens, hidden = h.shape
@@ -607,8 +615,9 @@ def moe_rows(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: 
     if (w_up.shape[2] != hidden or w_down.shape != (experts, hidden, ff) or act.shape != (tokens * top, ff)
             or out.shape != (tokens, hidden) or chosen.shape[0] != tokens or weight.shape != chosen.shape):
         raise KernelError("moe_rows: shapes disagree")
+    _channel_scale(out_scale, hidden, "moe_rows")
     _check(_moe().cisr_moe_rows(_p(h), _p(w_up), _p(w_down), dtype_code(h.dtype), _p(chosen), _p(weight), tokens, hidden, ff, top,
-                                _p(act), _p(out), _stream()), "moe_rows", own=2)
+                                _p(act), _p(out_scale), _p(out), _stream()), "moe_rows", own=2)
     return out
 
 
@@ -653,19 +662,22 @@ def moe_gather(h: torch.Tensor, src_token: torch.Tensor, sorted_h: torch.Tensor)
     return sorted_h
 
 
-def moe_combine(sorted_out: torch.Tensor, row_of: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t] = sum over k of weight[t, k] * sorted_out[row_of[t * top + k]], in the order of k."""
+def moe_combine(sorted_out: torch.Tensor, row_of: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+                out_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = out_scale * sum over k of weight[t, k] * sorted_out[row_of[t * top + k]], in the order of k."""
     _need(sorted_out, torch.float32, "sorted_out", 2); _need(row_of, torch.int32, "row_of", 1); _need(weight, torch.float32, "weight", 2)
     _need(out, torch.float32, "out", 2)
     tokens, top = weight.shape
     if row_of.numel() != tokens * top or out.shape != (tokens, sorted_out.shape[1]):
         raise KernelError("moe_combine: shapes disagree")
-    _check(_moe().cisr_moe_combine(_p(sorted_out), _p(row_of), _p(weight), tokens, top, out.shape[1], _p(out), _stream()), "moe_combine")
+    _channel_scale(out_scale, out.shape[1], "moe_combine")
+    _check(_moe().cisr_moe_combine(_p(sorted_out), _p(row_of), _p(weight), tokens, top, out.shape[1], _p(out_scale), _p(out), _stream()),
+           "moe_combine")
     return out
 
 
 def moe_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
-                out: torch.Tensor) -> torch.Tensor:
+                out: torch.Tensor, out_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The same sum as `moe_rows` for many tokens: pairs sorted by expert on the device, activations gathered into that
     order, both products as grouped tcgen05 products (relu^2 as the first one's epilogue), rows summed per token with the
     router's weights in the router's order.  Nothing is read back to the host."""
@@ -684,7 +696,7 @@ def moe_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chose
     sorted_h = moe_gather(h, src_token, torch.empty((rows, hidden), dtype=torch.bfloat16, device=device))
     act = gemm_tcgen05_grouped(sorted_h, w_up, torch.empty((rows, ff), dtype=torch.bfloat16, device=device), tile_group, tokens * top)
     sorted_out = gemm_tcgen05_grouped(act, w_down, torch.empty((rows, hidden), dtype=torch.float32, device=device), tile_group, tokens * top)
-    return moe_combine(sorted_out, row_of, weight, out)
+    return moe_combine(sorted_out, row_of, weight, out, out_scale)
 
 
 # ------------------------------------------------------------------ sampling
@@ -1134,7 +1146,7 @@ _DESCRIBE = {
     "moe_rows": lambda h, w_up, w_down, chosen, *a, **kw: (int(h.shape[0]), int(w_up.shape[0]), int(w_up.shape[1]), int(w_up.shape[2]), int(chosen.shape[1])),
     "moe_sort": lambda chosen, experts, *a: (int(chosen.shape[0]), int(chosen.shape[1]), int(experts)),
     "moe_gather": lambda h, src_token, sorted_h: (int(sorted_h.shape[0]), int(sorted_h.shape[1])),
-    "moe_combine": lambda sorted_out, row_of, weight, out: (int(out.shape[0]), int(weight.shape[1]), int(out.shape[1])),
+    "moe_combine": lambda sorted_out, row_of, weight, out, out_scale=None: (int(out.shape[0]), int(weight.shape[1]), int(out.shape[1])),
     "gemm_tcgen05_grouped": lambda a, w, out, tile_group, rows_in_use=None:
         (int(rows_in_use or a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2]), out.dtype == torch.bfloat16),
     "gemm_heads": lambda a, w, out, w_is_nk: (int(a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2])),

@@ -71,7 +71,9 @@ class ChannelScale(Part):
 @register(ARRANGEMENTS, "pre_norm_scaled")
 class PreNormScaledBlock:
     """x += s1 * mixer(norm1(x)); x += s2 * feed_forward(norm2(x)), with s1, s2 one factor per channel; the feed-forward
-    half may be absent.  The scaled add of each output is made by the norm kernel that follows it."""
+    half may be absent.  The scaled add of each output is made by the norm kernel that follows it; a feed-forward that
+    says `applies_output_scale` multiplies by s2 in its own last kernel instead, and its output is then pending like any
+    other (so the next layer's first product may take the add and the norm into its prologue)."""
 
     def __init__(self, spec: LayerSpec, dtype: torch.dtype):
         self.spec = spec
@@ -97,5 +99,9 @@ class PreNormScaledBlock:
         mixed = self._run(self.mixer, PendingNorm(stream, self.mixer_norm, self.dtype), ctx, cache)
         stream.pending, stream.pending_scale = mixed, self.mixer_scale.weight
         if self.feed_forward is not None:
-            out = self._run(self.feed_forward, PendingNorm(stream, self.feed_forward_norm, self.dtype), ctx)
-            stream.pending, stream.pending_scale = out, self.feed_forward_scale.weight
+            h = PendingNorm(stream, self.feed_forward_norm, self.dtype)
+            if getattr(self.feed_forward, "applies_output_scale", False):
+                stream.pending = self._run(self.feed_forward, h, ctx, self.feed_forward_scale.weight)
+            else:
+                out = self._run(self.feed_forward, h, ctx)
+                stream.pending, stream.pending_scale = out, self.feed_forward_scale.weight

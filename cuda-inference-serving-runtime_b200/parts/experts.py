@@ -29,6 +29,8 @@ class RoutedExperts(FeedForward):
     """params: hidden_size, expert_size, experts, top, groups, keep, route_scale, activation, names (local tensor names:
     router, and up / down with {} for the expert's number)."""
 
+    applies_output_scale = True      # forward(h, ctx, out_scale): a per-channel layer scale is the epilogue of the last kernel
+
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
         self.hidden = int(spec["hidden_size"])
@@ -74,11 +76,11 @@ class RoutedExperts(FeedForward):
         kernels.moe_select(logits, self.top, self.groups, self.keep, self.route_scale, chosen, weight)
         return chosen, weight
 
-    def forward(self, h, ctx):
+    def forward(self, h, ctx, out_scale=None):
         tokens = h.shape[0]
         chosen, weight = self.route(h)
         out = torch.empty((tokens, self.hidden), dtype=torch.float32, device=h.device)
         if kernels.moe_grouped_ok(h, self.up, self.top):
-            return kernels.moe_grouped(h, self.up, self.down, chosen, weight, out)     # many tokens: sorted by expert, tcgen05
+            return kernels.moe_grouped(h, self.up, self.down, chosen, weight, out, out_scale)     # many tokens: sorted by expert, tcgen05
         act = torch.empty((tokens * self.top, self.ff), dtype=self.dtype, device=h.device)
-        return kernels.moe_rows(h, self.up, self.down, chosen, weight, act, out)
+        return kernels.moe_rows(h, self.up, self.down, chosen, weight, act, out, out_scale)

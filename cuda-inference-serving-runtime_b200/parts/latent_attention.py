@@ -30,7 +30,7 @@ from ..config.spec import CacheUse
 from ..ops import kernels
 from .attention import ATTENTION_PLAN_KEY, attention_step_plan, paged_attention
 from .base import MIXERS, POSITIONS, Mixer, TensorNeed, build_part, register
-from .linear import linear
+from .linear import as_tensor, linear, norm_fusable
 
 ROW_STEP = 16          # cache rows are padded to a multiple of this (the attention kernels' head sizes)
 DEFAULT_NAMES = {"q": "q_proj.weight", "q_down": "q_down.weight", "q_norm": "q_norm.weight", "q_up": "q_up.weight",
@@ -45,6 +45,7 @@ class LatentAttention(Mixer):
     names (local tensor names of q, q_down, q_norm, q_up, kv_down, kv_norm, k_up, v_up, gate, out)."""
 
     graph_safe = True
+    accepts_pending_norm = True
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
@@ -122,7 +123,15 @@ class LatentAttention(Mixer):
         tokens, H, device = ctx.n_tokens, self.heads, ctx.device
         rot = self.position.rotation(ctx)
         table = dict(cos=rot.cos, sin=rot.sin, rot_half=rot.rot_half, interleaved=rot.interleaved)
-        proj = linear(h, self.w_in)                                            # float [tokens, stacked rows]
+        if norm_fusable(h, tokens, self.w_in):
+            # few tokens: the residual add and the norm are the prologue of the stacked input product
+            proj = torch.empty((tokens, self.w_in.shape[0]), dtype=torch.float32, device=device)
+            x_out = h.new_stream_buffer()
+            kernels.skinny_gemm(self.w_in, tokens, x=h.x, delta=h.delta, norm_w=h.weight, eps=h.eps, x_out=x_out,
+                                epilogue=kernels.EPI_PLAIN, out=proj)
+            h.done(x_out)
+        else:
+            proj = linear(as_tensor(h), self.w_in)                             # float [tokens, stacked rows]
         cq = torch.empty((tokens, self.q_rank), dtype=self.dtype, device=device) if self.q_rank else None
         kernels.latent_rows(proj, 0, self.q_rank, self.q_norm, cq, self.c_col, self.kv_rank, self.kv_norm, self.eps,
                             cache=cache.k if cache.write else None, token_req=ctx.token_req, positions=ctx.positions,
