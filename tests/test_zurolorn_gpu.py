@@ -164,6 +164,38 @@ def test_latent_row_and_query_kernels(dtype, interleaved):
     assert (q_rows[..., kv_rank + rot:] == 0).all() and (q_rows[..., :kv_rank] == 7).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("interleaved, gate", [(False, True), (True, False)])
+def test_few_token_kernels_around_the_attention(dtype, interleaved, gate):
+    """The row kernels of decode steps: queries carried into the latent's basis (with their rotated part), and the value
+    matrix applied to the weighted sum of cache rows (with the gate), against the plain formulas."""
+    from cisr_b200.ops import kernels
+    T, heads, plain, rot, kv_rank, vdim, row = 3, 5, 24, 12, 40, 28, 64
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(T, heads * (plain + rot) + 5, generator=g)
+    k_up = (torch.randn(heads, plain, kv_rank, generator=g) / plain ** 0.5).to(dtype)
+    positions = torch.tensor([0, 77, 1030])
+    angle = positions.to(F)[:, None] * torch.tensor([500.0 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=F)
+    cos, sin = torch.cos(angle).float().cuda(), torch.sin(angle).float().cuda()
+    q_rows = torch.full((T, heads, row), 3.0, dtype=dtype, device="cuda")
+    kernels.latent_absorb(q.cuda(), 0, heads, plain, cos, sin, rot // 2, interleaved, k_up.cuda(), q_rows, kv_rank)
+    qh = q[:, :heads * (plain + rot)].view(T, heads, plain + rot)
+    want = torch.einsum("thd,hdr->thr", qh[..., :plain].to(dtype).to(F), k_up.to(F))
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(q_rows[..., :kv_rank].cpu().to(F), want, atol=tol, rtol=tol)
+    assert torch.allclose(q_rows[..., kv_rank:kv_rank + rot].cpu().to(F), pz.rotate(qh[..., plain:].to(F), positions, 500.0, rot, interleaved), atol=tol, rtol=tol)
+    assert (q_rows[..., kv_rank + rot:] == 0).all()
+    mixed = torch.randn(T, heads, row, generator=g).to(dtype)
+    v_up = (torch.randn(heads, vdim, kv_rank, generator=g) / kv_rank ** 0.5).to(dtype)
+    gates = torch.randn(T, 9 + heads * vdim, generator=g)
+    out = torch.empty((T, heads * vdim), dtype=dtype, device="cuda")
+    kernels.latent_values(mixed.cuda(), v_up.cuda(), gates.cuda() if gate else None, 9, out)
+    want = torch.einsum("thr,hjr->thj", mixed[..., :kv_rank].to(F), v_up.to(F)).reshape(T, heads * vdim)
+    if gate:
+        want = want * torch.sigmoid(gates[:, 9:].to(F))
+    assert torch.allclose(out.cpu().to(F), want, atol=tol, rtol=tol)
+
+
 def one_layer(kind, mlp, loop=None):
     m = zm.mixer(kind, 3, 24, 8, 40, 48, 4321.0, q_rank=36)
     cfg = {"architecture": "Zurolorn", "vocab": 50, "width": 88, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-5}, "logit_scale": 2.0,
@@ -230,6 +262,28 @@ def test_long_decoding_crosses_many_pages(dtype, tmp_path_factory):
     steps += [{"step": i - 2, "entries": [{"id": "long", "tokens": [tokens[i]], "want": [0]}], "end": []} for i in range(3, len(tokens))]
     got = replay.run_steps(stepper_for(model, steps), steps)
     replay.compare(got, {"long": tokens}, reference, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_from_captured_graphs(dtype, tmp_path_factory):
+    """Decode steps replayed from CUDA graphs (two requests side by side, contexts crossing a graph's context bucket) give the
+    plain implementation's logits like steps launched directly."""
+    from cisr_b200 import StepEntry, Stepper
+    cfg, weights, path, model, _, _ = setup("zc", dtype, tmp_path_factory)
+    requests = {"u": zm.random_tokens(cfg, 90, 5), "v": zm.random_tokens(cfg, 61, 6)}
+    reference = {rid: pz.forward(cfg, weights, t).numpy() for rid, t in requests.items()}
+    stepper = Stepper(model, n_pages=12, page_size=16, max_slots=2, graph=True)
+    assert stepper.graphs is not None, "the mixers of this design are safe to capture"
+    got, heads = {}, {"u": 40, "v": 11}
+    for rid, tokens in requests.items():
+        stepper.create(rid)
+        stepper.step([StepEntry(rid, tokens[:heads[rid]], [])])
+    for i in range(50):
+        logits = stepper.step([StepEntry(rid, [requests[rid][heads[rid] + i]], [0]) for rid in requests]).cpu().numpy()
+        for row, rid in enumerate(requests):
+            got[(rid, heads[rid] + i)] = logits[row].copy()
+    stepper.check_kernels()
+    replay.compare(got, requests, reference, dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
