@@ -4,8 +4,9 @@ from .spec import CacheUse, LayerSpec, ModelSpec, PartSpec, RunEntry
 from .registry import ARCHITECTURES, Architecture, architecture_for, register_architecture
 from .llama import LlamaConfig      # registers LlamaForCausalLM
 from .zurolorn import ZurolornConfig    # registers Zurolorn
+from .ronolorn import RonolornConfig    # registers Ronolorn
 from .presets import preset, preset_dict, preset_names
 
-__all__ = ["CacheUse", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "LlamaConfig", "ZurolornConfig",
+__all__ = ["CacheUse", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "LlamaConfig", "ZurolornConfig", "RonolornConfig",
            "ARCHITECTURES", "Architecture", "architecture_for", "register_architecture",
            "preset", "preset_dict", "preset_names"]

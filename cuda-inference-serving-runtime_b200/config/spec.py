@@ -94,6 +94,7 @@ class ModelSpec:
     eos_token_ids: Tuple[int, ...] = ()
     pass_steps: Optional[PartSpec] = None        # per-pass vectors added to the stream where a run entry names a row
     pass_steps_prefix: str = ""
+    stream: PartSpec = PartSpec("single")        # what carries the residual through the layers: one vector per token, or several
 
     def validate(self) -> None:
         if not self.layers or not self.run:

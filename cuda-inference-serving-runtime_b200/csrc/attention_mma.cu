@@ -120,7 +120,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
                         const bf16* __restrict__ v_cache, const int* __restrict__ req_slot,
                         const int* __restrict__ block_table, int table_width, const int* __restrict__ tile_req,
                         const int* __restrict__ tile_q0, const int* __restrict__ q_start, const int* __restrict__ q_len,
-                        const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window) {
+                        const int* __restrict__ ctx_len, int hq, int hkv, int page_size, float scale, int window, float sink) {
     CISR_TRACE_SCOPE(TRACE_ATTN_PREFILL);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][LDS]
@@ -323,6 +323,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
             }
         }
         if (row < rows) {
+            if (sink > -INFINITY) l += exp2f(sink * LOG2E - m_use);     // the sink: one more term of the denominator, no value
             const float inv = 1.f / l;
             bf16* dst = out + ((size_t)(tok0 + row) * hq + head) * D + 2 * (lane & 3);
 #pragma unroll
@@ -902,7 +903,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 // are computed once into shared memory and the sum runs over the ranges in their fixed order.
 __global__ void attn_merge_kernel(const float* __restrict__ partial, const float* __restrict__ stats,
                                   bf16* __restrict__ out, const int* __restrict__ dec_req,
-                                  const int* __restrict__ q_start, int hq, int n_splits) {
+                                  const int* __restrict__ q_start, int hq, int n_splits, float sink) {
     CISR_TRACE_SCOPE(TRACE_ATTN_MERGE);
     extern __shared__ float weights[];            // [n_splits] weights, then [n_splits] weighted denominators
     __shared__ float scratch[32];
@@ -939,6 +940,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ partial, const float
     if (d >= D) return;
     float den = 0.f, num = 0.f;                   // every thread sums in the same order: the same denominator in all
     for (int s = 0; s < n_splits; ++s) den += weights[n_splits + s];
+    if (den > 0.f && sink > -INFINITY) den += expf(sink - m);          // the sink: one more term of the denominator, no value
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
         const float w = j < n_splits ? weights[j] : 0.f;
@@ -967,7 +969,7 @@ CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache,
                                   const int* req_slot, const int* block_table, int table_width, const int* tile_req,
                                   const int* tile_q0, int n_tiles, const int* q_start, const int* q_len,
                                   const int* ctx_len, int hq, int hkv, int page_size, float scale, int window,
-                                  void* stream) {
+                                  float sink, void* stream) {
     if (n_tiles <= 0) return 0;
     if (hq % hkv) return -2;
     const size_t smem = PREFILL_SMEM + sizeof(int) * ((size_t)table_width + 4);    // a tile's key range spans at most the table
@@ -980,14 +982,14 @@ CISR_EXPORT int cisr_attn_prefill(const void* q, void* out, const void* k_cache,
     }
     return launch_kernel(attn_prefill_mma_kernel, dim3(n_tiles, hq), dim3(PREFILL_THREADS), smem, (cudaStream_t)stream, g_pdl,
                          (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, req_slot, block_table,
-                         table_width, tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window);
+                         table_width, tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv, page_size, scale, window, sink);
 }
 
 CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
                                  const int* req_slot, const int* block_table, int table_width, const int* dec_req,
                                  int n_dec, const int* q_start, const int* ctx_len, float* partial, float* stats, int hq,
                                  int hkv, int page_size, float scale, int window, int split_size, int n_splits,
-                                 int merge, void* stream) {
+                                 int merge, float sink, void* stream) {
     // merge == 0: the ranges' partial sums and statistics are left in `partial` and `stats` for the caller's own merge
     // (merge_proj.cu merges them in the prologue of the output projection); `out` is then not written.
     if (n_dec <= 0) return 0;
@@ -1011,7 +1013,7 @@ CISR_EXPORT int cisr_attn_decode(const void* q, void* out, const void* k_cache, 
     }
     if (!merge) return 0;
     return launch_kernel(attn_merge_kernel, dim3(n_dec, hq), dim3(D <= 64 ? 64 : 128), sizeof(float) * 2 * (size_t)n_splits, s, g_pdl,
-                         (const float*)partial, (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_splits);
+                         (const float*)partial, (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_splits, sink);
 }
 
 // 1 when this library has the variant that stages tiles by tensor-map copies, and it takes this page and range size.
@@ -1041,7 +1043,8 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
                                      const int* req_slot, const int* block_table, int table_width, const int* dec_req,
                                      int n_dec, const int* q_start, const int* ctx_len, float* partial, float* stats,
                                      int hq, int hkv, int page_size, float scale, int window, int split_size,
-                                     int n_splits, int merge, void* stream) {
+                                     int n_splits, int merge, float sink, void* stream) {
+    // `sink` (-inf: none) is added to the denominator by the merge kernel, so the ranges are never merged inside a cluster then
     if (n_dec <= 0) return 0;
     if (!g_encode || !g_error) return -13;
     if (!merge && g_clusters) return -2;      // the caller's own merge needs every range's partial sum
@@ -1075,7 +1078,7 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
     int cluster = 1;
     size_t smem = smem_plain;
     static int resident[17] = {};            // per cluster size: 0 unknown, 1 yes, -1 no (asked with the largest shared memory)
-    for (int c = 16; c >= 2 && g_clusters; --c) {
+    for (int c = 16; c >= 2 && g_clusters && !(sink > -INFINITY); --c) {
         if (n_splits % c) continue;
         const size_t need = smem_plain + sizeof(float) * (size_t)c * rows_max * ((D + c - 1) / c + 2);
         if (need > SMEM_CAP) continue;
@@ -1119,7 +1122,7 @@ CISR_EXPORT int cisr_attn_decode_tma(const void* q, void* out, const void* k_cac
     }
     if ((n_parts == 1 && cluster > 1) || !merge) return 0;
     return launch_kernel(attn_merge_kernel, dim3(n_dec, hq), dim3(D <= 64 ? 64 : 128), sizeof(float) * 2 * (size_t)n_parts, s, g_pdl,
-                         (const float*)partial, (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_parts);
+                         (const float*)partial, (const float*)stats, (bf16*)out, dec_req, q_start, hq, n_parts, sink);
 }
 
 #ifdef DEC_TRACE

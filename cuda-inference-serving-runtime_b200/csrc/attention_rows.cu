@@ -1,0 +1,135 @@
+// From the stacked q | k | v projection of a step to the operands of the paged attention kernels, one CTA per token:
+// biases, a norm over a whole projection, rotation of part of each head, heads padded to the width the attention
+// kernels are built for, keys and values written into their cache pages.
+//
+//   row   = proj[t] + bias                                   (bias null: none)
+//   qn    = q_norm ? q / sqrt(mean(q^2) + eps) * q_norm : q  (the mean runs over ALL query heads of the token at once)
+//   kn    = k_norm ? k / sqrt(mean(k^2) + eps) * k_norm : k
+//   q_out[t][h] = [rotate(qn_h) | 0]                          (key_dim wide, padded with zeros to D)
+//   k_cache[page][g][off] = [rotate(kn_g) | 0]
+//   v_cache[page][g][off] = [v_g | 0]  with v from its own columns, or (v_col < 0) the key as projected: with its bias,
+//                                      before norm and rotation; value_dim = key_dim then
+//
+// The first 2 * rot_half coordinates of a head turn; pairs are (i, i + rot_half) or, interleaved, (2i, 2i + 1).
+// The tables hold cos and sin per (token, pair), already multiplied by whatever factor the encoding wants.
+// Float arithmetic; one rounding where q_out and the cache have a narrower type.
+#include "common.cuh"
+
+static bool g_pdl = false;
+CISR_EXPORT void cisr_attention_rows_set_pdl(int on) { g_pdl = on != 0; }
+
+namespace {
+__device__ __forceinline__ float turned(const float* head, const float* w, float inv, int d, int rot_half, int interleaved,
+                                        const float* cs, const float* sn) {
+    // value d of a head after the optional norm (common factor inv, per-coordinate weight w) and the rotation
+    float v = head[d] * inv * (w ? w[d] : 1.f);
+    if (d < 2 * rot_half) {
+        int f, other; bool first;
+        if (interleaved) { f = d >> 1; first = !(d & 1); other = first ? d + 1 : d - 1; }
+        else { first = d < rot_half; f = first ? d : d - rot_half; other = first ? d + rot_half : d - rot_half; }
+        const float o = head[other] * inv * (w ? w[other] : 1.f);
+        v = first ? v * cs[f] - o * sn[f] : v * cs[f] + o * sn[f];
+    }
+    return v;
+}
+
+template <typename QT, typename CT>
+__global__ void __launch_bounds__(256)
+attention_rows_kernel(const float* __restrict__ proj, int row_stride, int k_col, int v_col, const float* __restrict__ bias,
+                      const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_half, int interleaved,
+                      QT* __restrict__ q_out, CT* __restrict__ k_cache, CT* __restrict__ v_cache,
+                      const int* __restrict__ token_req, const int* __restrict__ positions, const int* __restrict__ req_slot,
+                      const int* __restrict__ block_table, int table_width, int page_size, int hq, int hkv, int key_dim,
+                      int value_dim, int D, int n_cols) {
+    extern __shared__ float row[];            // n_cols floats: the token's projection with its bias
+    __shared__ float scratch[32];
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int slot = req_slot[token_req[t]];
+    pdl_wait();
+    const float* src = proj + (size_t)t * row_stride;
+    for (int i = threadIdx.x; i < n_cols; i += blockDim.x) row[i] = src[i] + (bias ? bias[i] : 0.f);
+    __syncthreads();
+    const int nq = hq * key_dim, nk = hkv * key_dim;
+    float inv_q = 1.f, inv_k = 1.f;
+    if (q_norm) {
+        float sq = 0.f;
+        for (int i = threadIdx.x; i < nq; i += blockDim.x) sq += row[i] * row[i];
+        inv_q = 1.f / sqrtf(block_sum(sq, scratch) / (float)nq + eps);
+    }
+    if (k_norm) {
+        float sq = 0.f;
+        for (int i = threadIdx.x; i < nk; i += blockDim.x) sq += row[k_col + i] * row[k_col + i];
+        inv_k = 1.f / sqrtf(block_sum(sq, scratch) / (float)nk + eps);
+    }
+    const float* cs = cos_t ? cos_t + (size_t)t * rot_half : nullptr;
+    const float* sn = sin_t ? sin_t + (size_t)t * rot_half : nullptr;
+    for (int i = threadIdx.x; i < hq * D; i += blockDim.x) {
+        const int h = i / D, d = i - h * D;
+        float v = 0.f;
+        if (d < key_dim) v = turned(row + h * key_dim, q_norm ? q_norm + h * key_dim : nullptr, inv_q, d, rot_half, interleaved, cs, sn);
+        q_out[((size_t)t * hq + h) * D + d] = from_float<QT>(v);
+    }
+    if (!k_cache) return;
+    const int page = block_table[(size_t)slot * table_width + pos / page_size];
+    if (page < 0) return;                     // the host reserves a page before every write; never follow a missing entry
+    const int off = pos % page_size;
+    for (int i = threadIdx.x; i < hkv * D; i += blockDim.x) {
+        const int g = i / D, d = i - g * D;
+        float kv = 0.f, vv = 0.f;
+        if (d < key_dim) kv = turned(row + k_col + g * key_dim, k_norm ? k_norm + g * key_dim : nullptr, inv_k, d, rot_half, interleaved, cs, sn);
+        if (d < value_dim) vv = v_col >= 0 ? row[v_col + g * value_dim + d] : row[k_col + g * key_dim + d];
+        const size_t dst = (((size_t)page * hkv + g) * page_size + off) * D + d;
+        k_cache[dst] = from_float<CT>(kv);
+        v_cache[dst] = from_float<CT>(vv);
+    }
+}
+
+// out[t][c] += bias[c]
+__global__ void bias_add_kernel(float* __restrict__ out, const float* __restrict__ bias, int cols, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) out[i] += bias[i % cols];
+}
+}  // namespace
+
+CISR_EXPORT int cisr_attention_rows(const float* proj, int row_stride, int k_col, int v_col, const float* bias, const float* q_norm,
+                                    const float* k_norm, float eps, const float* cos_t, const float* sin_t, int rot_half,
+                                    int interleaved, void* q_out, int q_dtype, void* k_cache, void* v_cache, int cache_dtype,
+                                    const int* token_req, const int* positions, const int* req_slot, const int* block_table,
+                                    int table_width, int page_size, int hq, int hkv, int key_dim, int value_dim, int D, int tokens,
+                                    void* stream) {
+    if (tokens <= 0) return 0;
+    if (2 * rot_half > key_dim || rot_half < 0 || key_dim > D || value_dim > D || hq <= 0 || hkv <= 0) return -2;
+    if (v_col < 0 && value_dim != key_dim) return -2;
+    if (rot_half && (!cos_t || !sin_t)) return -2;
+    const int n_cols = v_col >= 0 ? v_col + hkv * value_dim : k_col + hkv * key_dim;
+    if (n_cols > row_stride) return -2;
+    const size_t smem = sizeof(float) * (size_t)n_cols;
+    if (smem > 200 * 1024) return -3;
+    cudaStream_t s = (cudaStream_t)stream;
+#define CISR_ROWS(QT, CT)                                                                                                 \
+    do {                                                                                                                  \
+        static size_t configured = 48 * 1024;                                                                             \
+        if (smem > configured) {                                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(attention_rows_kernel<QT, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e;                                                                          \
+            configured = smem;                                                                                            \
+        }                                                                                                                 \
+        return launch_kernel(attention_rows_kernel<QT, CT>, dim3(tokens), dim3(256), smem, s, g_pdl, proj, row_stride, k_col, v_col, bias, \
+                             q_norm, k_norm, eps, cos_t, sin_t, rot_half, interleaved, (QT*)q_out, (CT*)k_cache, (CT*)v_cache,   \
+                             token_req, positions, req_slot, block_table, table_width, page_size, hq, hkv, key_dim, value_dim, D, n_cols); \
+    } while (0)
+    if (q_dtype == CISR_BF16 && cache_dtype == CISR_BF16) CISR_ROWS(__nv_bfloat16, __nv_bfloat16);
+    if (q_dtype == CISR_F32 && cache_dtype == CISR_F32) CISR_ROWS(float, float);
+    return -2;
+#undef CISR_ROWS
+}
+
+CISR_EXPORT int cisr_bias_add(float* out, const float* bias, int rows, int cols, void* stream) {
+    const size_t total = (size_t)rows * cols;
+    if (!total) return 0;
+    bias_add_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(out, bias, cols, total);
+    return launch_status();
+}

@@ -269,11 +269,43 @@ CISR_EXPORT int cisr_swiglu(const float* gate_up, void* out, int out_dtype, int 
     return launch_status();
 }
 
+// ---------------------------------------------------------------- activation of a dense feed-forward
+// out[t, c] = act(x[t, c]) for c < cols, 0 for cols <= c < out_cols (columns that pad the next product's K).
+// kind 0: max(z, 0)^2;  1: gelu, tanh form, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)));  2: silu.
+template <typename OT>
+__global__ void activation_kernel(const float* __restrict__ x, OT* __restrict__ out, int cols, int out_cols, int kind, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / out_cols;
+    const int c = (int)(i - t * out_cols);
+    float v = 0.f;
+    if (c < cols) {
+        const float z = x[t * cols + c];
+        if (kind == 0) { const float r = fmaxf(z, 0.f); v = r * r; }
+        else if (kind == 1) v = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        else v = z / (1.f + expf(-z));
+    }
+    out[i] = from_float<OT>(v);
+}
+
+CISR_EXPORT int cisr_activation(const float* x, void* out, int out_dtype, int tokens, int cols, int out_cols, int kind, void* stream) {
+    const size_t total = (size_t)tokens * out_cols;
+    if (!total) return 0;
+    if (kind < 0 || kind > 2 || out_cols < cols) return -2;
+    const dim3 grid((unsigned)((total + 255) / 256));
+    if (out_dtype == CISR_BF16)
+        return launch_kernel(activation_kernel<__nv_bfloat16>, grid, dim3(256), 0, (cudaStream_t)stream, g_pdl, x, (__nv_bfloat16*)out, cols, out_cols, kind, total);
+    return launch_kernel(activation_kernel<float>, grid, dim3(256), 0, (cudaStream_t)stream, g_pdl, x, (float*)out, cols, out_cols, kind, total);
+}
+
 // ---------------------------------------------------------------- rotary tables
-// cos/sin [T, half] in float from double angles pos * inv_freq[i]; run once per step
+// cos/sin [T, half] in float from double angles pos * inv_freq[i], both times `magnitude` (1 unless the encoding
+// scales its tables); run once per step
 // and shared by every layer that rotates with the same theta and width.
 __global__ void rotary_table_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
-                                    float* __restrict__ cos_out, float* __restrict__ sin_out, int half, int total) {
+                                    float* __restrict__ cos_out, float* __restrict__ sin_out, int half, int total, double magnitude) {
     CISR_TRACE_SCOPE(TRACE_ROTARY_TABLE);
     // No early start for the kernels after this one: the fused q/k/v kernels read these tables before their own wait
     // on their predecessor, so whatever runs between this kernel and them must not start before the tables are written.
@@ -284,16 +316,16 @@ __global__ void rotary_table_kernel(const int* __restrict__ positions, const dou
     const int t = i / half, f = i - t * half;
     double s, c;
     sincos((double)positions[t] * inv_freq[f], &s, &c);
-    cos_out[i] = (float)c;
-    sin_out[i] = (float)s;
+    cos_out[i] = (float)(c * magnitude);
+    sin_out[i] = (float)(s * magnitude);
 }
 
 CISR_EXPORT int cisr_rotary_tables(const int* positions, const double* inv_freq, float* cos_out, float* sin_out,
-                                   int tokens, int half, void* stream) {
+                                   int tokens, int half, double magnitude, void* stream) {
     const int total = tokens * half;
     if (total <= 0) return 0;
     return launch_kernel(rotary_table_kernel, dim3((total + 127) / 128), dim3(128), 0, (cudaStream_t)stream, g_pdl, positions, inv_freq,
-                         cos_out, sin_out, half, total);
+                         cos_out, sin_out, half, total, magnitude);
 }
 
 // ---------------------------------------------------------------- rotation + cache write

@@ -15,7 +15,7 @@ import torch
 
 from ..cache import CacheManager
 from ..config import ModelSpec, architecture_for
-from ..parts import ARRANGEMENTS, EMBEDDINGS, HEADS, NORMS, ResidualStream, TensorNeed, build_part
+from ..parts import ARRANGEMENTS, EMBEDDINGS, HEADS, NORMS, STREAMS, TensorNeed, build_part
 from ..ops import build as kernel_build
 
 DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, torch.float32: torch.float32,
@@ -50,6 +50,10 @@ class Model:
         self.final_norm = build_part(NORMS, spec.final_norm, self.dtype, "norm")
         self.head = build_part(HEADS, spec.head, self.dtype, "head")
         self.pass_steps = None if spec.pass_steps is None else build_part(EMBEDDINGS, spec.pass_steps, self.dtype, "per-pass vectors")
+        if spec.stream.kind not in STREAMS:
+            raise KeyError(f"no residual stream registered as {spec.stream.kind!r}")
+        self.stream_class = STREAMS[spec.stream.kind]
+        self.layer_probe = None      # when set: called with (run entry index, stream) after every layer (tests, debugging)
         self.loaded = False
 
     # ---------------------------------------------------------------- tensors
@@ -88,6 +92,11 @@ class Model:
                 key = repr(job)
                 if key not in seen:
                     seen.add(key)
+                    jobs.append(job)
+        for layer in self.layers:
+            for job in (layer.kernel_jobs() if hasattr(layer, "kernel_jobs") else []):
+                if repr(job) not in seen:
+                    seen.add(repr(job))
                     jobs.append(job)
         jobs.append(("sampling.cu", {}, ()))
         return jobs
@@ -135,17 +144,16 @@ class Model:
         """Run the step's tokens through every run entry; float logits [wanted rows, vocab]."""
         for part in self.step_beginners():
             part.begin_step(ctx)
-        stream = ResidualStream(self.embedding.forward(ctx.token_ids))
+        stream = self.stream_class(self.embedding.forward(ctx.token_ids), self.spec.stream)
         for index, entry in enumerate(self.spec.run):
             if entry.pass_step is not None:
                 self.pass_steps.add_to(stream, entry.pass_step)
             self.layers[entry.layer].forward(stream, ctx, cache.binding(index, reads_from=entry.cache_of))
+            if self.layer_probe is not None:
+                self.layer_probe(index, stream)
         if ctx.logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
-        scale = stream.pending_scale
-        extra = {} if scale is None else {"delta_scale": scale}
-        h = self.final_norm.forward(stream.x, stream.take_pending(), self.dtype, rows=ctx.logit_rows, write_back=False, **extra)
-        return self.head.forward(h)
+        return self.head.forward(stream.finish(self.final_norm, self.dtype, ctx.logit_rows))
 
     # ---------------------------------------------------------------- construction
     @classmethod

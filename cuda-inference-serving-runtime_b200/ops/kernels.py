@@ -82,6 +82,7 @@ def _elementwise():
         lib.cisr_table_update.restype = ctypes.c_int
         lib.cisr_stream_add.restype = ctypes.c_int
         lib.cisr_scale.restype = ctypes.c_int
+        lib.cisr_activation.restype = ctypes.c_int
         lib._typed = True
     return lib
 
@@ -164,13 +165,31 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def rotary_tables(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+ACTIVATIONS = {"relu_squared": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
+    """out[:, :n] = act(x) for float x [tokens, n]; columns of out beyond n (padding of the next product's K) get zeros."""
+    _need(x, torch.float32, "x", 2); _need(out, None, "out", 2)
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"unknown activation {kind!r}; known: {', '.join(sorted(ACTIVATIONS))}")
+    if out.shape[0] != x.shape[0] or out.shape[1] < x.shape[1]:
+        raise KernelError("activation: out must have x's rows and at least its columns")
+    _check(_elementwise().cisr_activation(_p(x), _p(out), dtype_code(out.dtype), x.shape[0], x.shape[1], out.shape[1],
+                                          ACTIVATIONS[kind], _stream()), "activation")
+    return out
+
+
+def rotary_tables(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                  magnitude: float = 1.0) -> None:
+    """cos, sin [tokens, pairs] = magnitude * cos / sin(position * inv_freq), angles in float64."""
     _need(positions, torch.int32, "positions", 1); _need(inv_freq, torch.float64, "inv_freq", 1)
     _need(cos, torch.float32, "cos", 2); _need(sin, torch.float32, "sin", 2)
     tokens, half = cos.shape
     if positions.numel() != tokens or inv_freq.numel() != half or sin.shape != cos.shape:
         raise KernelError("rotary_tables: shapes disagree")
-    _check(_elementwise().cisr_rotary_tables(_p(positions), _p(inv_freq), _p(cos), _p(sin), tokens, half, _stream()),
+    _check(_elementwise().cisr_rotary_tables(_p(positions), _p(inv_freq), _p(cos), _p(sin), tokens, half,
+                                             ctypes.c_double(magnitude), _stream()),
            "rotary_tables")
 
 
@@ -321,9 +340,15 @@ def attn_prefill_wide_ok(q: torch.Tensor, k_cache: torch.Tensor, page_size: int)
             and k_cache.shape[0] * k_cache.shape[1] * page_size < 2 ** 31)
 
 
+def _sink(sink: Optional[float]) -> ctypes.c_float:
+    """A softmax sink as the kernels take it: one more term exp(sink) in the denominator that carries no value; None: none."""
+    return ctypes.c_float(float("-inf") if sink is None else float(sink))
+
+
 def attn_prefill_wide(q, out, k_cache, v_cache, req_slot, block_table, wide_req, wide_q0, q_start, q_len, ctx_len, hq, hkv,
-                      page_size, scale, window) -> None:
-    """Attention of portions on tcgen05: q, out [tokens, hq, D]; tiles of 128 queries as (request, first query)."""
+                      page_size, scale, window, sink: Optional[float] = None) -> None:
+    """Attention of portions on tcgen05: q, out [tokens, hq, D]; tiles of 128 queries as (request, first query).
+    `sink`: see `_sink`."""
     dim = k_cache.shape[-1]
     _need(q, torch.bfloat16, "q", 3); _need(out, torch.bfloat16, "out", 3); _need(k_cache, torch.bfloat16, "k_cache", 4)
     _need(v_cache, torch.bfloat16, "v_cache", 4)
@@ -336,14 +361,14 @@ def attn_prefill_wide(q, out, k_cache, v_cache, req_slot, block_table, wide_req,
     _check(lib.cisr_attn_prefill_tcgen05(_p(q), _p(out), q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0], _p(req_slot),
                                          _p(block_table), block_table.shape[1], _p(wide_req), _p(wide_q0), wide_req.numel(),
                                          _p(q_start), _p(q_len), _p(ctx_len), hq, hkv, page_size, ctypes.c_float(scale),
-                                         int(window or 0), _stream()), "attn_prefill_wide")
+                                         int(window or 0), _sink(sink), _stream()), "attn_prefill_wide")
 
 
 PREFILL_TILE = 64
 
 
 def attn_prefill(q, out, k_cache, v_cache, req_slot, block_table, tile_req, tile_q0, q_start, q_len, ctx_len, hq, hkv,
-                 page_size, scale, window, kind: str = "auto") -> None:
+                 page_size, scale, window, kind: str = "auto", sink: Optional[float] = None) -> None:
     """Attention of portions: q, out [tokens, hq, D]; tiles list (request, first query of the tile)."""
     dim = k_cache.shape[-1]
     _need(q, k_cache.dtype, "q"); _need(out, k_cache.dtype, "out"); _need(k_cache, None, "k_cache", 4)
@@ -354,11 +379,12 @@ def attn_prefill(q, out, k_cache, v_cache, req_slot, block_table, tile_req, tile
     lib = attention_library(dim, k_cache.dtype, kind)
     _check(lib.cisr_attn_prefill(_p(q), _p(out), _p(k_cache), _p(v_cache), _p(req_slot), _p(block_table), block_table.shape[1],
                                  _p(tile_req), _p(tile_q0), tile_req.numel(), _p(q_start), _p(q_len), _p(ctx_len),
-                                 hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), _stream()), "attn_prefill")
+                                 hq, hkv, page_size, ctypes.c_float(scale), int(window or 0), _sink(sink), _stream()), "attn_prefill")
 
 
 def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec, q_start, ctx_len, partial, stats, hq, hkv,
-                page_size, scale, window, split_size, n_splits, kind: str = "auto", staging: str = "auto", merge: bool = True) -> None:
+                page_size, scale, window, split_size, n_splits, kind: str = "auto", staging: str = "auto", merge: bool = True,
+                sink: Optional[float] = None) -> None:
     """Attention of single new tokens, split over key ranges of `split_size`, merged into out.
 
     `merge=False` (tensor-core kernels only) leaves the ranges' partial sums in `partial` and `stats` and does not write
@@ -381,6 +407,9 @@ def attn_decode(q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec,
         tail.append(int(merge))
     elif not merge:
         raise KernelError("attn_decode: only the tensor-core kernels leave the merge to the caller")
+    if sink is not None and not merge:
+        raise KernelError("attn_decode: the sink is added by the merge kernel; a caller that merges itself cannot ask for one")
+    tail.append(_sink(sink))
     tail.append(_stream())
     if staging not in ("auto", "tensor_map", "gather"):
         raise KernelError(f"unknown staging {staging!r}")
@@ -439,6 +468,207 @@ def merge_out_proj(partial: torch.Tensor, stats: torch.Tensor, n_splits: int, de
     status = _merge_proj().cisr_merge_proj(_p(partial), _p(stats), n_splits, _p(dec_req), _p(q_start), n_dec, hq, dim, _p(w),
                                            w.shape[0], w.shape[1], _p(out), int(bool(accumulate)), _stream())
     _check(status, "merge_out_proj")
+    return out
+
+
+# ------------------------------------------------------------------ several residual streams (hyper-connections) and their norm
+_hyper_state = {}
+NORM_KINDS = {"layer": 0, "rms": 1}
+
+
+def _hyper():
+    lib = _hyper_state.get("lib")
+    if lib is None:
+        lib = load_library("hyper.cu")
+        for name in ("cisr_hyper_mix_norm", "cisr_hyper_sum", "cisr_hyper_max_streams"):
+            getattr(lib, name).restype = ctypes.c_int
+        lib.cisr_hyper_set_pdl(int(_pdl_state["on"]))
+        _hyper_state["lib"] = lib
+    return lib
+
+
+def hyper_jobs():
+    return [("hyper.cu", {}, ())]
+
+
+HYPER_MAX_STREAMS = 16
+
+
+def hyper_mix_norm(source: torch.Tensor, streams: torch.Tensor, n_streams: int, *, y: Optional[torch.Tensor] = None,
+                   bias: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None, out_w: Optional[torch.Tensor] = None,
+                   in_w: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
+                   norm_kind: str = "layer", h: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+                   store: bool = True) -> Optional[torch.Tensor]:
+    """One pass over the residual streams of every token (see csrc/hyper.cu): with `y` (float [tokens, hidden], plus the
+    per-channel `bias`) the streams become x'_t = sum_s mix[s, t] x_s + out_w[t] * (y + bias); then h = norm(sum_t in_w[t]
+    x'_t) * norm_w.  `source` is float [tokens, n_streams, hidden], or [tokens, hidden] read as every stream; `streams`
+    [tokens, n_streams, hidden] receives x' when `store` (it may be `source`).  mix None: identity; out_w, in_w None:
+    ones.  `rows` picks the tokens that become rows of h; h None: the streams only."""
+    _need(source, torch.float32, "source"); _need(streams, torch.float32, "streams", 3)
+    tokens, s_count, hidden = streams.shape
+    if s_count != n_streams or not 1 <= n_streams <= HYPER_MAX_STREAMS:
+        raise KernelError(f"hyper_mix_norm: streams must be [tokens, {n_streams}, hidden] with at most {HYPER_MAX_STREAMS} streams")
+    source_is_row = source.dim() == 2
+    if tuple(source.shape) not in ((tokens, hidden), (tokens, n_streams, hidden)):
+        raise KernelError("hyper_mix_norm: source must be [tokens, hidden] or [tokens, streams, hidden]")
+    for name, t, n in (("y", y, tokens * hidden), ("bias", bias, hidden), ("mix", mix, n_streams * n_streams),
+                       ("out_w", out_w, n_streams), ("in_w", in_w, n_streams)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.numel() != n:
+                raise KernelError(f"hyper_mix_norm: {name} has {t.numel()} elements, {n} are needed")
+    if bias is not None and y is None:
+        raise KernelError("hyper_mix_norm: a bias without an output to add it to")
+    if norm_kind not in NORM_KINDS:
+        raise KernelError(f"unknown norm kind {norm_kind!r}")
+    n_rows = tokens
+    if h is not None:
+        _need(h, None, "h", 2); _need(norm_w, None, "norm_w", 1)
+        if norm_w.numel() != hidden or h.shape[1] != hidden:
+            raise KernelError("hyper_mix_norm: width mismatch")
+        n_rows = h.shape[0]
+    if rows is not None:
+        _need(rows, torch.int32, "rows", 1)
+        if h is None or rows.numel() != n_rows:
+            raise KernelError("hyper_mix_norm: one row index per row of h is needed")
+    elif n_rows != tokens:
+        raise KernelError("hyper_mix_norm: h and the streams differ in rows")
+    _check(_hyper().cisr_hyper_mix_norm(
+        _p(source), int(source_is_row), _p(streams), _p(y), _p(bias), _p(mix), _p(out_w), _p(in_w), _p(norm_w),
+        dtype_code(norm_w.dtype) if norm_w is not None else 0, _p(h), dtype_code(h.dtype) if h is not None else 0, _p(rows), n_rows,
+        n_streams, hidden, ctypes.c_float(eps), NORM_KINDS[norm_kind], int(bool(store)), _stream()), "hyper_mix_norm")
+    return h
+
+
+def hyper_sum(streams: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = the sum of token t's streams."""
+    _need(streams, torch.float32, "streams", 3); _need(out, torch.float32, "out", 2)
+    tokens, n_streams, hidden = streams.shape
+    if out.shape != (tokens, hidden):
+        raise KernelError("hyper_sum: out must be [tokens, hidden]")
+    _check(_hyper().cisr_hyper_sum(_p(streams), _p(out), tokens, n_streams, hidden, _stream()), "hyper_sum")
+    return out
+
+
+# ------------------------------------------------------------------ the rows of a stacked q | k | v projection
+_rows_state = {}
+
+
+def _attention_rows():
+    lib = _rows_state.get("lib")
+    if lib is None:
+        lib = load_library("attention_rows.cu")
+        lib.cisr_attention_rows.restype = ctypes.c_int
+        lib.cisr_bias_add.restype = ctypes.c_int
+        lib.cisr_attention_rows_set_pdl(int(_pdl_state["on"]))
+        _rows_state["lib"] = lib
+    return lib
+
+
+def attention_rows_jobs():
+    return [("attention_rows.cu", {}, ())]
+
+
+def attention_rows(proj: torch.Tensor, k_col: int, v_col: int, *, bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor],
+                   k_norm: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_half: int,
+                   interleaved: bool, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_req: torch.Tensor,
+                   positions: torch.Tensor, req_slot: torch.Tensor, block_table: torch.Tensor, page_size: int, hq: int, hkv: int,
+                   key_dim: int, value_dim: int) -> None:
+    """proj float [tokens, cols] holds q at column 0, k at `k_col`, v at `v_col` (`v_col` < 0: the values are the keys as
+    projected).  Adds `bias` (float [cols]), norms q and k over their whole projection (`q_norm`, `k_norm`: float weights of
+    that size, or None), rotates, pads the heads to the cache's width D, writes q_out [tokens, hq, D] and the key and value
+    rows into their pages ([pages, hkv, page_size, D]).  See csrc/attention_rows.cu."""
+    _need(proj, torch.float32, "proj", 2); _need(q_out, None, "q_out", 3); _need(k_cache, q_out.dtype, "k_cache", 4)
+    _need(v_cache, q_out.dtype, "v_cache", 4)
+    tokens, cols = proj.shape
+    width = k_cache.shape[-1]
+    if tuple(q_out.shape) != (tokens, hq, width) or tuple(k_cache.shape[1:]) != (hkv, page_size, width) or v_cache.shape != k_cache.shape:
+        raise KernelError("attention_rows: q_out must be [tokens, hq, D] and the caches [pages, hkv, page_size, D]")
+    for name, t, n in (("bias", bias, cols), ("q_norm", q_norm, hq * key_dim), ("k_norm", k_norm, hkv * key_dim)):
+        if t is not None:
+            _need(t, torch.float32, name, 1)
+            if t.numel() != n:
+                raise KernelError(f"attention_rows: {name} has {t.numel()} elements, {n} are needed")
+    if rot_half:
+        _need(cos, torch.float32, "cos", 2); _need(sin, torch.float32, "sin", 2)
+        if cos.shape != (tokens, rot_half) or sin.shape != cos.shape:
+            raise KernelError("attention_rows: rotary tables must be [tokens, rot_half]")
+    for name, t in (("token_req", token_req), ("positions", positions), ("req_slot", req_slot), ("block_table", block_table)):
+        _need(t, torch.int32, name)
+    _check(_attention_rows().cisr_attention_rows(
+        _p(proj), cols, k_col, v_col, _p(bias), _p(q_norm), _p(k_norm), ctypes.c_float(eps), _p(cos if rot_half else None),
+        _p(sin if rot_half else None), rot_half, int(interleaved), _p(q_out), dtype_code(q_out.dtype), _p(k_cache), _p(v_cache),
+        dtype_code(k_cache.dtype), _p(token_req), _p(positions), _p(req_slot), _p(block_table), block_table.shape[1], page_size,
+        hq, hkv, key_dim, value_dim, width, tokens, _stream()), "attention_rows")
+
+
+def bias_add(out: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """out[t, :] += bias, in place (float)."""
+    _need(out, torch.float32, "out", 2); _need(bias, torch.float32, "bias", 1)
+    if bias.numel() != out.shape[1]:
+        raise KernelError("bias_add: one bias per column is needed")
+    _check(_attention_rows().cisr_bias_add(_p(out), _p(bias), out.shape[0], out.shape[1], _stream()), "bias_add")
+    return out
+
+
+# ------------------------------------------------------------------ the gated delta rule
+_delta_state = {}
+DELTA_MAX_KEY_DIM = 256
+
+
+def _delta():
+    lib = _delta_state.get("lib")
+    if lib is None:
+        lib = load_library("delta.cu")
+        for name in ("cisr_delta_prepare", "cisr_delta_keep", "cisr_delta_recurrence", "cisr_delta_output", "cisr_delta_max_key_dim"):
+            getattr(lib, name).restype = ctypes.c_int
+        assert lib.cisr_delta_max_key_dim() == DELTA_MAX_KEY_DIM
+        lib.cisr_delta_set_pdl(int(_pdl_state["on"]))
+        _delta_state["lib"] = lib
+    return lib
+
+
+def delta_jobs():
+    return [("delta.cu", {}, ())]
+
+
+def delta_step(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+               norm_w: torch.Tensor, eps: float, norm_eps: float, token_req: torch.Tensor, req_slot: torch.Tensor, q_start: torch.Tensor,
+               q_len: torch.Tensor, n_req: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, out: torch.Tensor) -> torch.Tensor:
+    """The gated delta rule for a step's tokens (see csrc/delta.cu).  proj float [tokens, cols]: the stacked projection
+    q | k | v | gate | b | a (cols may be padded beyond them); conv_w float [2 * kv_heads * key_dim + heads * value_dim, taps];
+    state float [slots, heads * key_dim * value_dim + (taps - 1) * conv channels] is read and advanced for the step's
+    requests; out [tokens, >= heads * value_dim] in the operand type of the output projection."""
+    _need(proj, torch.float32, "proj", 2); _need(conv_w, torch.float32, "conv_w", 2); _need(state, torch.float32, "state", 2)
+    for name, t in (("a_log", a_log), ("dt_bias", dt_bias), ("norm_w", norm_w)):
+        _need(t, torch.float32, name, 1)
+    for name, t in (("token_req", token_req), ("req_slot", req_slot), ("q_start", q_start), ("q_len", q_len)):
+        _need(t, torch.int32, name, 1)
+    _need(out, None, "out", 2)
+    tokens, cols = proj.shape
+    channels = 2 * kv_heads * key_dim + heads * value_dim
+    matrix = heads * key_dim * value_dim
+    if (tuple(conv_w.shape) != (channels, taps) or state.shape[1] != matrix + (taps - 1) * channels or a_log.numel() != heads
+            or dt_bias.numel() != heads or norm_w.numel() != value_dim or out.shape[0] != tokens or out.shape[1] < heads * value_dim
+            or cols < channels + heads * value_dim + 2 * heads or key_dim > DELTA_MAX_KEY_DIM):
+        raise KernelError("delta_step: shapes disagree")
+    device = proj.device
+    qkv = torch.empty((tokens, channels), dtype=torch.float32, device=device)
+    beta = torch.empty((tokens, heads), dtype=torch.float32, device=device)
+    decay = torch.empty((tokens, heads), dtype=torch.float32, device=device)
+    o = torch.empty((tokens, heads, value_dim), dtype=torch.float32, device=device)
+    lib, stride = _delta(), ctypes.c_longlong(state.shape[1])
+    keep_at = ctypes.c_longlong(matrix)
+    _check(lib.cisr_delta_prepare(_p(proj), cols, _p(conv_w), taps, _p(state), stride, keep_at, _p(a_log), _p(dt_bias), _p(token_req),
+                                  _p(req_slot), _p(q_start), _p(qkv), _p(beta), _p(decay), heads, kv_heads, key_dim, value_dim,
+                                  ctypes.c_float(norm_eps), tokens, _stream()), "delta_prepare")
+    if taps > 1:
+        _check(lib.cisr_delta_keep(_p(proj), cols, _p(state), stride, keep_at, _p(req_slot), _p(q_start), _p(q_len), taps, channels,
+                                   n_req, _stream()), "delta_keep")
+    _check(lib.cisr_delta_recurrence(_p(qkv), _p(beta), _p(decay), _p(state), stride, _p(req_slot), _p(q_start), _p(q_len), _p(o),
+                                     heads, kv_heads, key_dim, value_dim, n_req, _stream()), "delta_recurrence")
+    _check(lib.cisr_delta_output(_p(o), _p(proj), cols, channels, _p(norm_w), ctypes.c_float(eps), _p(out), dtype_code(out.dtype),
+                                 out.shape[1], heads, value_dim, tokens, _stream()), "delta_output")
     return out
 
 
@@ -848,6 +1078,12 @@ def set_pdl(on: bool) -> None:
         _latent_state["lib"].cisr_latent_set_pdl(int(on))
     if "lib" in _moe_state:
         _moe_state["lib"].cisr_moe_set_pdl(int(on))
+    if "lib" in _hyper_state:
+        _hyper_state["lib"].cisr_hyper_set_pdl(int(on))
+    if "lib" in _rows_state:
+        _rows_state["lib"].cisr_attention_rows_set_pdl(int(on))
+    if "lib" in _delta_state:
+        _delta_state["lib"].cisr_delta_set_pdl(int(on))
     if "lib" in _tcgen05_state:
         _tcgen05_state["lib"].cisr_gemm_tcgen05_set_pdl(int(on))
     for (source, _, _), lib in list(_attention_libs.items()):

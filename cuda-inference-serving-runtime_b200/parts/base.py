@@ -6,7 +6,8 @@ and the compute dtype.  It says which tensors it needs under local names
 No part knows which model or which layer it is in: checkpoint names are made by
 the model from the layer's prefix and the local name.
 
-Registries: NORMS, POSITIONS, MIXERS, FEED_FORWARDS, ARRANGEMENTS, EMBEDDINGS, HEADS.
+Registries: NORMS, POSITIONS, MIXERS, FEED_FORWARDS, ARRANGEMENTS, EMBEDDINGS, HEADS, STREAMS (the object that carries
+the residual stream through the layers: one vector per token, or several).
 `register(registry, kind)` is a class decorator; registering a kind twice is an error.
 """
 from __future__ import annotations
@@ -28,12 +29,14 @@ class TensorNeed:
     role "table": an integer table, kept as int32.
     `alias` names a tensor (by full checkpoint name) to use when this one is absent (a tied head).
     `init_std` is the spread seeded random weights are drawn with when the default does not suit the tensor (a router
-    whose scores must not all be alike).
+    whose scores must not all be alike); `init_mean` the value they are drawn around (a number, or "identity" for a
+    square table), where a vector's default of 1 does not suit it (a bias, a table of mixing weights).
     """
     shape: Tuple[int, ...]
     role: str = "matrix"
     alias: Optional[str] = None
     init_std: Optional[float] = None
+    init_mean: Any = None
 
 
 class Part:
@@ -187,6 +190,7 @@ FEED_FORWARDS: Dict[str, type] = {}
 ARRANGEMENTS: Dict[str, type] = {}
 EMBEDDINGS: Dict[str, type] = {}
 HEADS: Dict[str, type] = {}
+STREAMS: Dict[str, type] = {}
 
 
 def register(registry: Dict[str, type], kind: str):

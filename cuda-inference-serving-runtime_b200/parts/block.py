@@ -11,13 +11,14 @@ from typing import Optional
 import torch
 
 from ..config.spec import LayerSpec
-from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, Part, PendingNorm, TensorNeed, build_part, register
+from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, STREAMS, Part, PendingNorm, TensorNeed, build_part, register
 
 
+@register(STREAMS, "single")
 class ResidualStream:
     """The float residual stream x [tokens, hidden] and an output not added to it yet."""
 
-    def __init__(self, x: torch.Tensor):
+    def __init__(self, x: torch.Tensor, spec=None):
         self.x = x
         self.pending: Optional[torch.Tensor] = None
         self.pending_scale: Optional[torch.Tensor] = None    # per-channel factor the pending output is added with
@@ -27,6 +28,20 @@ class ResidualStream:
         pending, self.pending = self.pending, None
         self.pending_scale = None
         return pending
+
+    def finish(self, norm, dtype: torch.dtype, rows: torch.Tensor) -> torch.Tensor:
+        """The model's last step: norm(x + pending) at the wanted rows."""
+        scale = self.pending_scale
+        extra = {} if scale is None else {"delta_scale": scale}
+        return norm.forward(self.x, self.take_pending(), dtype, rows=rows, write_back=False, **extra)
+
+    def total(self) -> torch.Tensor:
+        """x with the pending output added, as a new tensor; the stream object stays as it was."""
+        x = self.x.clone()
+        if self.pending is not None:
+            from ..ops import kernels
+            kernels.stream_add(x, self.pending, self.pending_scale, None)
+        return x
 
 
 @register(ARRANGEMENTS, "pre_norm")

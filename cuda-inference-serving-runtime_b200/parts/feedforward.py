@@ -61,3 +61,45 @@ class SwiGLU(FeedForward):
             else:
                 kernels.swiglu(linear(hn, self.gate_up), act)
         return linear_to_stream(act, self.down, h0)
+
+
+def pad_columns(w: torch.Tensor, multiple: int) -> torch.Tensor:
+    """w [N, K] with zero columns appended until K is a multiple (the products take K in whole 16-byte groups)."""
+    extra = -w.shape[1] % multiple
+    return w.contiguous() if not extra else torch.nn.functional.pad(w, (0, extra)).contiguous()
+
+
+@register(FEED_FORWARDS, "dense_mlp")
+class DenseMLP(FeedForward):
+    """down(act(up(h))) without a gate and without biases.  params: hidden_size, intermediate_size, activation
+    ("relu_squared": max(z, 0)^2, "gelu_tanh", "silu"); names (up, down).  The activation is taken in float on the
+    product's float sums and rounded once to the operand type of the second product."""
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.activation = spec.get("activation", "relu_squared")
+        if self.activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"unknown activation {self.activation!r}")
+        self.names = dict({"up": "up", "down": "down"}, **dict(spec.get("names", {})))
+        self.up = None
+        self.down = None
+
+    def tensor_needs(self) -> Dict[str, TensorNeed]:
+        return {self.names["up"]: TensorNeed((self.inter, self.hidden)),
+                self.names["down"]: TensorNeed((self.hidden, self.inter))}
+
+    def load(self, tensors):
+        self.up = tensors[self.names["up"]].contiguous()
+        self.down = pad_columns(tensors[self.names["down"]], 8)
+
+    def kernel_jobs(self):
+        return ([("elementwise.cu", {}, ())] + kernels.gemm_jobs(self.dtype)
+                + (kernels.skinny_jobs() if self.dtype == torch.bfloat16 else []))
+
+    def forward(self, h, ctx):
+        h = as_tensor(h)
+        act = torch.empty((h.shape[0], self.down.shape[1]), dtype=self.dtype, device=h.device)
+        kernels.activation(linear(h, self.up), act, self.activation)
+        return linear(act, self.down)

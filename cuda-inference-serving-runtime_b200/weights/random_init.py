@@ -40,7 +40,12 @@ def draw(name: str, need: TensorNeed, seed: int, device=None) -> torch.Tensor:
         return torch.zeros(shape, dtype=torch.int32)
     values = torch.randn(shape, generator=gen, dtype=torch.float32, device=device if on_device else "cpu")
     if need.role == "vector":
-        return 1.0 + VECTOR_STD * values
+        spread = VECTOR_STD if need.init_std is None else need.init_std
+        if isinstance(need.init_mean, str):
+            if need.init_mean != "identity" or len(shape) != 2 or shape[0] != shape[1]:
+                raise ValueError(f"{name}: init_mean {need.init_mean!r} needs a square table")
+            return torch.eye(shape[0], dtype=torch.float32, device=values.device) + spread * values
+        return (1.0 if need.init_mean is None else float(need.init_mean)) + spread * values
     return (MATRIX_STD if need.init_std is None else need.init_std) * values
 
 
