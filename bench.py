@@ -27,7 +27,8 @@ every request holding about 4096 tokens of context while it decodes.  Prints ONE
 --workload mixed: the continuous-batching workload (by default the SmolLM2-1.7B sizes, 64 requests with prompts
 of 128 to 2048 tokens, 256 generated tokens each) through the scheduler with graphs on; prints total, prefill
 and decode tokens per second, launch counts, graph statistics and a roofline for the whole run.
---designs SIZES: Zurolorn (latent attention, routed experts) beside the Llama shape of equal size at the named widths:
+--designs SIZES [--design zurolorn|ronolorn]: Zurolorn (latent attention, routed experts) or Ronolorn (windowed attention,
+gated delta rule, several residual streams) beside the Llama shape of equal size at the named widths:
 prompt and decode tokens per second of both, and per kind of kernel the device time and the distance from the roofline.
 --impl reference: the reference's own stock code on the same decode workload (see reference_arm).
 
@@ -446,6 +447,24 @@ def design_pair(width: int, layers: int, heads: int, ff_active: int, experts: in
     return zur, llama
 
 
+def ronolorn_pair(width: int, layers: int, heads: int, ff_active: int, experts: int = 0, top: int = 0, vocab: int = 32000):
+    """A Ronolorn shape and the Llama shape of equal size beside it: the same width, layers, query heads of 64 with a
+    quarter as many key heads, and vocabulary; layers in the order attention, attention_2, delta, attention over four
+    streams; the dense feed-forward (two matrices) is one and a half times as wide as the gated one (three), so both hold
+    the same weights.  Windows of 1024 keys."""
+    kv = max(1, heads // 4)
+    rot = {"base": 10000.0, "dims": 64}
+    att = {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024}, "rot": rot}
+    att2 = dict(att, kv_heads=1, rot=dict(rot, scaling={"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}))
+    delta = {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 64, "conv": 4}
+    order = [("attention", att), ("attention_2", att2), ("delta", delta), ("attention", att)]
+    mlp = {"kind": "dense", "ff": ff_active * 3 // 2}
+    rono = {"architecture": "Ronolorn", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "streams": 4,
+            "max_positions": 8192,
+            "layers": [{"type": order[i % 4][0], "mixer": order[i % 4][1], "mlp": mlp} for i in range(layers)]}
+    return rono, design_pair(width, layers, heads, ff_active, max(experts, 4), max(top, 1), vocab)[1]
+
+
 DESIGN_SIZES = {"1024": (1024, 8, 16, 2048, 16, 4), "2048": (2048, 8, 32, 4096, 32, 4), "4096": (4096, 4, 32, 8192, 64, 8)}
 KERNEL_KIND = {   # which kernels of the two designs are alike
     "gemm_tcgen05": "product, many tokens", "gemm_library": "product, many tokens", "gemm_tcgen05_swiglu": "feed-forward product, many tokens",
@@ -454,7 +473,9 @@ KERNEL_KIND = {   # which kernels of the two designs are alike
     "attn_decode": "decode attention", "merge_out_proj": "product, few tokens", "add_rmsnorm": "norm", "embedding": "row kernels", "rope_store": "row kernels",
     "latent_rows": "row kernels", "latent_query": "row kernels", "latent_gate": "row kernels", "latent_absorb": "product per head",
     "latent_values": "product per head", "moe_select": "row kernels", "moe_gather": "row kernels",
-    "moe_combine": "row kernels", "moe_sort": "bookkeeping", "stream_add": "row kernels", "swiglu": "row kernels"}
+    "moe_combine": "row kernels", "moe_sort": "bookkeeping", "stream_add": "row kernels", "swiglu": "row kernels",
+    "hyper_mix_norm": "norm", "attention_rows": "row kernels", "activation": "row kernels", "delta_prepare": "row kernels",
+    "delta_output": "row kernels", "delta_keep": "bookkeeping", "delta_recurrence": "recurrence"}
 
 
 def generic_need(name: str, shape: tuple, cache_tokens: int, causal: int):
@@ -484,11 +505,31 @@ def generic_need(name: str, shape: tuple, cache_tokens: int, causal: int):
         n_dec, n, k, splits = shape
         return n * k * 2 + n_dec * splits * k * 4, 2.0 * n_dec * n * k
     if name == "attn_decode":
-        n_dec, hq, hkv, d, merge, one_plane = shape
+        n_dec, hq, hkv, d, merge, one_plane, window = shape
+        if window and n_dec:                      # a window of keys: what a request's token must read of its context
+            cache_tokens = n_dec * min(window, cache_tokens // n_dec)
         return cache_tokens * (1 if one_plane else 2) * hkv * d * 2, 4.0 * cache_tokens * hq * d
     if name in ("attn_prefill_wide", "attn_prefill"):
-        tokens, hq, hkv, d = shape
-        return 2 * tokens * (hq + 2 * hkv) * d * 2, 4.0 * hq * d * causal * (causal + 1) / 2
+        tokens, hq, hkv, d, window = shape
+        pairs = causal * (causal + 1) / 2 if not window or window >= causal else window * (window + 1) / 2 + (causal - window) * window
+        return 2 * tokens * (hq + 2 * hkv) * d * 2, 4.0 * hq * d * pairs
+    if name == "hyper_mix_norm":
+        rows, streams, hidden, added, stored, spread = shape
+        return rows * hidden * (4 * ((1 if spread else streams) + (streams if stored else 0) + (1 if added else 0)) + 2), 0.0
+    if name == "attention_rows":
+        return shape[0] * shape[1] * 6, 0.0
+    if name == "activation":
+        return shape[0] * shape[1] * 6, 0.0
+    if name == "delta_prepare":
+        tokens, channels, taps = shape
+        return tokens * channels * 8, 2.0 * tokens * channels * taps
+    if name == "delta_output":
+        return shape[0] * shape[1] * 10, 0.0
+    if name == "delta_recurrence":
+        # the state once in and once out per request, the tokens' operands once; the arithmetic runs on the CUDA cores in float
+        # (seven operations per state element and token), which the tensor-core peak does not describe: bytes only
+        tokens, n_req, heads, kvh, dk, dv = shape
+        return (n_req * 2 * heads * dk * dv + tokens * (2 * kvh * dk + 2 * heads * dv + 2 * heads)) * 4, 0.0
     if name == "add_rmsnorm":
         rows, hidden, added = shape
         return rows * hidden * (4 + (8 if added else 0) + 2), 0.0
@@ -566,7 +607,8 @@ def design_comparison(args, hbm_gbs: float, burst_tflops: float, peak_source: st
 
     sizes = [s for s in args.designs.split(",") if s]
     batch, context, prompt = args.batch, min(args.context, 2048), PREFILL_TOKENS
-    line = {"designs": "zurolorn beside llama at equal size", "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
+    pair = ronolorn_pair if args.design == "ronolorn" else design_pair
+    line = {"designs": f"{args.design} beside llama at equal size", "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
             "batch": batch, "context": context, "prompt_tokens": prompt, "peaks": peak_source, "sizes": {}}
     sampler = ClockSampler().start()
     for size in sizes:
@@ -574,7 +616,7 @@ def design_comparison(args, hbm_gbs: float, burst_tflops: float, peak_source: st
             raise SystemExit(f"--designs takes sizes from {', '.join(DESIGN_SIZES)}")
         width, layers, heads, ff_active, experts, top = DESIGN_SIZES[size]
         entry = {"width": width, "layers": layers, "heads": heads, "feed_forward_active": ff_active, "experts": experts, "top": top}
-        for name, raw in zip(("zurolorn", "llama"), design_pair(width, layers, heads, ff_active, experts, top)):
+        for name, raw in zip((args.design, "llama"), pair(width, layers, heads, ff_active, experts, top)):
             model = Model.from_config(raw, seed=args.seed, dtype="bfloat16")
             prefill_ms = prefill_run(model, prompt, args.seed)
             d = device_decode(model, batch, context, min(args.steps, 64), args.warmup, args.seed, min_seconds=0.2)
@@ -828,6 +870,9 @@ def main() -> int:
     parser.add_argument("--designs", metavar="SIZES", default=None,
                         help="instead of the default workload: Zurolorn beside the Llama shape of equal size, prompt and decode, at "
                              "the named widths (comma-separated, from 1024, 2048, 4096)")
+    parser.add_argument("--design", choices=["zurolorn", "ronolorn"], default="zurolorn",
+                        help="--designs: which design stands beside the Llama shape (ronolorn: windowed attention, gated delta rule, "
+                             "four residual streams, dense feed-forward)")
     args = parser.parse_args()
     if args.workload == "mixed" and "--preset" not in " ".join(sys.argv):
         args.preset = "smollm2-1.7b"

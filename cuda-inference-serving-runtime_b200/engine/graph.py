@@ -84,6 +84,19 @@ def _align(n: int) -> int:
     return (n + 3) & ~3
 
 
+def keep_states(cache) -> list:
+    """Copies of the per-request state tensors (a recurrent mixer's), taken before a warm-up run outside a graph.  Such a run
+    writes the same keys and values into the pages as the replay after it, which is harmless, but it advances a state that the
+    replay advances again: the state is put back after the warm-up (`put_states_back`)."""
+    return [None if g.storage is None else g.storage.clone() for g in cache.state_groups]
+
+
+def put_states_back(cache, kept: list) -> None:
+    for g, saved in zip(cache.state_groups, kept):
+        if saved is not None:
+            g.storage.copy_(saved)
+
+
 class DecodeGraph:
     """One captured decode step for `rows` padded rows and contexts up to `ctx_bucket`."""
 
@@ -220,12 +233,14 @@ class DecodeGraph:
         """Warm up once outside the graph (library set-up, kernel attributes), then capture.  `warm_up=False`: a graph
         for the same number of rows was captured before, so the same kernels have run already."""
         if warm_up:
+            kept = keep_states(self.stepper.cache)
             stream = torch.cuda.Stream()
             stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(stream):
                 self._run(advance=False)
             torch.cuda.current_stream().wait_stream(stream)
             torch.cuda.synchronize()
+            put_states_back(self.stepper.cache, kept)
         before = dict(kernels.LAUNCHES)
         self.graph = torch.cuda.CUDAGraph()
         pdl = os.environ.get("CISR_PDL", "1") != "0"
@@ -279,12 +294,14 @@ class ShapeGraph:
     def run(self, ctx, update_views) -> torch.Tensor:
         """`ctx` and `update_views` view this shape's static buffers, already filled and sent for this step."""
         if self.graph is None:
+            kept = keep_states(self.stepper.cache)
             stream = torch.cuda.Stream()
             stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(stream):
                 self._run(ctx, update_views)        # warm-up outside the graph; writes the same cache entries the replay will
             torch.cuda.current_stream().wait_stream(stream)
             torch.cuda.synchronize()
+            put_states_back(self.stepper.cache, kept)
             before = dict(kernels.LAUNCHES)
             self.graph = torch.cuda.CUDAGraph()
             kernels.set_pdl(os.environ.get("CISR_PDL", "1") != "0")

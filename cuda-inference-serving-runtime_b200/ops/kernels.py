@@ -632,6 +632,34 @@ def delta_jobs():
     return [("delta.cu", {}, ())]
 
 
+def delta_prepare(proj, conv_w, taps, state, a_log, dt_bias, token_req, req_slot, q_start, qkv, beta, decay, heads, kv_heads,
+                  key_dim, value_dim, norm_eps) -> None:
+    """Convolution over time with the request's kept inputs, silu, unit norms of q and k, beta and the decay, per token."""
+    _check(_delta().cisr_delta_prepare(_p(proj), proj.shape[1], _p(conv_w), taps, _p(state), ctypes.c_longlong(state.shape[1]),
+                                       ctypes.c_longlong(heads * key_dim * value_dim), _p(a_log), _p(dt_bias), _p(token_req),
+                                       _p(req_slot), _p(q_start), _p(qkv), _p(beta), _p(decay), heads, kv_heads, key_dim, value_dim,
+                                       ctypes.c_float(norm_eps), proj.shape[0], _stream()), "delta_prepare")
+
+
+def delta_keep(proj, state, req_slot, q_start, q_len, n_req, taps, channels, matrix) -> None:
+    """The last taps - 1 convolution inputs of every request of the step become its kept inputs."""
+    _check(_delta().cisr_delta_keep(_p(proj), proj.shape[1], _p(state), ctypes.c_longlong(state.shape[1]), ctypes.c_longlong(matrix),
+                                    _p(req_slot), _p(q_start), _p(q_len), taps, channels, n_req, _stream()), "delta_keep")
+
+
+def delta_recurrence(qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim) -> None:
+    """The state's walk over each request's tokens, in order; o [tokens, heads, value_dim] float."""
+    _check(_delta().cisr_delta_recurrence(_p(qkv), _p(beta), _p(decay), _p(state), ctypes.c_longlong(state.shape[1]), _p(req_slot),
+                                          _p(q_start), _p(q_len), _p(o), heads, kv_heads, key_dim, value_dim, n_req, _stream()),
+           "delta_recurrence")
+
+
+def delta_output(o, proj, gate_col, norm_w, eps, out, heads, value_dim) -> None:
+    """out = o / rms(o) * norm_w * silu(gate) per head, rounded to out's type."""
+    _check(_delta().cisr_delta_output(_p(o), _p(proj), proj.shape[1], gate_col, _p(norm_w), ctypes.c_float(eps), _p(out),
+                                      dtype_code(out.dtype), out.shape[1], heads, value_dim, o.shape[0], _stream()), "delta_output")
+
+
 def delta_step(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
                norm_w: torch.Tensor, eps: float, norm_eps: float, token_req: torch.Tensor, req_slot: torch.Tensor, q_start: torch.Tensor,
                q_len: torch.Tensor, n_req: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, out: torch.Tensor) -> torch.Tensor:
@@ -657,18 +685,12 @@ def delta_step(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch
     beta = torch.empty((tokens, heads), dtype=torch.float32, device=device)
     decay = torch.empty((tokens, heads), dtype=torch.float32, device=device)
     o = torch.empty((tokens, heads, value_dim), dtype=torch.float32, device=device)
-    lib, stride = _delta(), ctypes.c_longlong(state.shape[1])
-    keep_at = ctypes.c_longlong(matrix)
-    _check(lib.cisr_delta_prepare(_p(proj), cols, _p(conv_w), taps, _p(state), stride, keep_at, _p(a_log), _p(dt_bias), _p(token_req),
-                                  _p(req_slot), _p(q_start), _p(qkv), _p(beta), _p(decay), heads, kv_heads, key_dim, value_dim,
-                                  ctypes.c_float(norm_eps), tokens, _stream()), "delta_prepare")
+    delta_prepare(proj, conv_w, taps, state, a_log, dt_bias, token_req, req_slot, q_start, qkv, beta, decay, heads, kv_heads, key_dim,
+                  value_dim, norm_eps)
     if taps > 1:
-        _check(lib.cisr_delta_keep(_p(proj), cols, _p(state), stride, keep_at, _p(req_slot), _p(q_start), _p(q_len), taps, channels,
-                                   n_req, _stream()), "delta_keep")
-    _check(lib.cisr_delta_recurrence(_p(qkv), _p(beta), _p(decay), _p(state), stride, _p(req_slot), _p(q_start), _p(q_len), _p(o),
-                                     heads, kv_heads, key_dim, value_dim, n_req, _stream()), "delta_recurrence")
-    _check(lib.cisr_delta_output(_p(o), _p(proj), cols, channels, _p(norm_w), ctypes.c_float(eps), _p(out), dtype_code(out.dtype),
-                                 out.shape[1], heads, value_dim, tokens, _stream()), "delta_output")
+        delta_keep(proj, state, req_slot, q_start, q_len, n_req, taps, channels, matrix)
+    delta_recurrence(qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim)
+    delta_output(o, proj, channels, norm_w, eps, out, heads, value_dim)
     return out
 
 
@@ -1387,14 +1409,28 @@ _DESCRIBE = {
         (int(rows_in_use or a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2]), out.dtype == torch.bfloat16),
     "gemm_heads": lambda a, w, out, w_is_nk: (int(a.shape[0]), int(w.shape[0]), int(w.shape[1]), int(w.shape[2])),
     "swiglu": lambda gate_up, out: (int(out.shape[0]), int(out.shape[1])),
-    "rotary_tables": lambda positions, inv_freq, cos, sin: (int(cos.shape[0]), int(cos.shape[1])),
+    "rotary_tables": lambda positions, inv_freq, cos, sin, magnitude=1.0: (int(cos.shape[0]), int(cos.shape[1])),
+    "hyper_mix_norm": lambda source, streams, n_streams, **kw:
+        (int(streams.shape[0] if kw.get("h") is None else kw["h"].shape[0]), int(n_streams), int(streams.shape[2]), kw.get("y") is not None,
+         bool(kw.get("store", True)), source.dim() == 2),
+    "hyper_sum": lambda streams, out: tuple(int(n) for n in streams.shape),
+    "attention_rows": lambda proj, *a, **kw: (int(proj.shape[0]), int(proj.shape[1])),
+    "bias_add": lambda out, bias: (int(out.shape[0]), int(out.shape[1])),
+    "activation": lambda x, out, kind: (int(x.shape[0]), int(x.shape[1])),
+    "delta_prepare": lambda proj, conv_w, taps, *a: (int(proj.shape[0]), int(conv_w.shape[0]), int(taps)),
+    "delta_keep": lambda proj, state, req_slot, q_start, q_len, n_req, taps, channels, matrix: (int(n_req), int(channels), int(taps)),
+    "delta_recurrence": lambda qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim:
+        (int(qkv.shape[0]), int(n_req), int(heads), int(kv_heads), int(key_dim), int(value_dim)),
+    "delta_output": lambda o, proj, *a: (int(o.shape[0]), int(o.shape[1] * o.shape[2])),
     "rope_store": lambda proj, *rest, **kw: (int(proj.shape[0]), int(proj.shape[1])),
     "page_copy": lambda *a, **kw: (),
     "table_update": lambda *a, **kw: (),
-    "attn_prefill_wide": lambda q, out, k_cache, *rest, **kw: (int(q.shape[0]), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2])),
-    "attn_prefill": lambda q, out, k_cache, *rest, **kw: (int(q.shape[0]), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2])),
+    # (tokens, query heads, key heads, head width, window or 0); the window is the sixteenth positional argument of both
+    "attn_prefill_wide": lambda q, out, k_cache, *rest, **kw: (int(q.shape[0]), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2]), int(rest[12] or 0)),
+    "attn_prefill": lambda q, out, k_cache, *rest, **kw: (int(q.shape[0]), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2]), int(rest[12] or 0)),
     "attn_decode": lambda q, out, k_cache, v_cache, req_slot, block_table, dec_req, n_dec, *rest, **kw:
-        (int(n_dec), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2]), bool(kw.get("merge", True)), k_cache.data_ptr() == v_cache.data_ptr()),
+        (int(n_dec), int(q.shape[1]), int(k_cache.shape[1]), int(q.shape[2]), bool(kw.get("merge", True)), k_cache.data_ptr() == v_cache.data_ptr(),
+         int(rest[8] or 0)),
     "merge_out_proj": lambda partial, stats, n_splits, dec_req, q_start, n_dec, hq, dim, w, out, **kw:
         (int(n_dec), int(w.shape[0]), int(w.shape[1]), int(n_splits)),
     "sample": lambda logits, *rest, **kw: (int(logits.shape[0]), int(logits.shape[1])),

@@ -32,8 +32,9 @@ UNIT_NORM_EPS = 1e-6
 class GatedDelta(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, key_dim, value_dim, conv (taps), eps (of the output norm), names."""
 
-    # A captured decode step is run once or twice before its first replay; that would advance the state more than once.
-    graph_safe = False
+    # forward reads the step through device tensors only.  A captured step's warm-up run outside the graph would advance the
+    # state once too often: the graph code keeps the state tensors and puts them back after it (engine/graph.py).
+    graph_safe = True
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
