@@ -11,10 +11,10 @@
 //                    (x / sqrt(sum x^2 + norm_eps), q times key_dim^-1/2), beta = sigmoid(.), and
 //                    decay = exp(-exp(A_log) * softplus(a + dt_bias)).
 //   delta_keep       per request: the last taps - 1 convolution inputs become the request's kept inputs.
-//   delta_recurrence per (request, head, 8 value columns): one warp walks the portion's tokens in order.  A column of
-//                    S evolves on its own, so four lanes share a column (each holds a quarter of its rows in
-//                    registers) and the two dot products are finished by two shuffles.  Loads of the next token are
-//                    issued before the current token's arithmetic.
+//   delta_recurrence per (request, head, a few value columns): one warp walks the portion's tokens in order.  A column of
+//                    S evolves on its own, so 4 to 32 lanes share a column (each holds its share of the rows in
+//                    registers) and the two dot products are finished by shuffles.  The tokens' operands are staged
+//                    through shared memory a block of tokens ahead.
 //   delta_output     per (token, head): o / sqrt(mean(o^2) + eps) * norm_w * silu(gate), rounded to the operand type of
 //                    the output projection.
 // A request's row of the state tensor holds [heads][key_dim][value_dim] and then [taps - 1][conv channels], all float.
@@ -90,70 +90,131 @@ __global__ void delta_keep_kernel(const float* __restrict__ proj, int row_stride
     }
 }
 
-// R: rows of a column held by one lane (key_dim <= 4 * R); BUFS 2: the next token's operands are fetched into a second
-// set of registers before the current token's arithmetic (1 where two sets would not fit the register file)
-template <int R, int BUFS>
-__global__ void __launch_bounds__(32)
+// L lanes share a column of the state and each holds R of its rows in registers (key_dim <= L * R): row r is lane
+// r % L's.  A warp owns 32 / L columns.  The walk is a chain of dependent instructions, so a warp runs at a fraction of
+// the issue rate whatever else runs beside it; what counts is how few instructions a token costs it.  Eight warps form
+// a CTA and share the staged tokens (each thread copies a share of them); the host picks L = 8 unless the launch would
+// then have fewer CTAs than the device has SMs.  The tokens' operands come through shared memory in blocks of
+// STAGE_TOKENS tokens, two blocks in flight (cp.async), so the walk over the tokens waits for memory once per block and
+// not once per token: per token a row [k: dk][q: dk][beta][decay][v: the CTA's columns].
+constexpr int STAGE_TOKENS = 16;
+constexpr int DELTA_THREADS = 256;            // eight warps share the staged tokens; a CTA owns 256 / L columns of one head
+__host__ __device__ inline int stage_stride(int dk, int columns) { return 2 * dk + 2 + columns; }
+
+__device__ __forceinline__ void copy4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+template <int R, int L>
+__global__ void __launch_bounds__(DELTA_THREADS)
 delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
                         float* __restrict__ state, long long state_stride, const int* __restrict__ req_slot,
                         const int* __restrict__ q_start, const int* __restrict__ q_len, float* __restrict__ out,
                         int heads, int kvh, int dk, int dv) {
+    extern __shared__ float stage[];          // [2][STAGE_TOKENS][stage_stride(dk, columns of the CTA)]
     pdl_trigger();
+    constexpr int CPC = DELTA_THREADS / L;    // columns per CTA
     const int req = blockIdx.x, head = blockIdx.y;
-    const int lane = threadIdx.x, part = lane & 3;
-    const int col = blockIdx.z * 8 + (lane >> 2);
+    const int tid = threadIdx.x, part = tid % L, mine = tid / L;
+    const int col0 = blockIdx.z * CPC, col = col0 + mine;
     const bool live = col < dv;
     const int g = head / (heads / kvh);
     const int channels = 2 * kvh * dk + heads * dv;
     const int first = q_start[req], n = q_len[req];
     float* S = state + (size_t)req_slot[req] * state_stride + (size_t)head * dk * dv;
+    const int stride = stage_stride(dk, CPC), cols = min(CPC, dv - col0);
+    const int q_at = g * dk, k_at = kvh * dk + g * dk, v_at = 2 * kvh * dk + head * dv + col0;
+    const int per_token = 2 * dk + cols + 2;  // floats a token brings: k, q, the CTA's columns of v, beta, decay
     pdl_wait();
+    auto fetch = [&](int block, float* buf) {          // tokens [block * STAGE_TOKENS, ...) of the portion, by all threads
+        const int t0 = block * STAGE_TOKENS, count = min(STAGE_TOKENS, n - t0);
+        for (int i = tid; i < count * per_token; i += DELTA_THREADS) {
+            const int j = i / per_token, e = i - j * per_token;
+            const size_t t = (size_t)(first + t0 + j);
+            const float* src;
+            int at;
+            if (e < dk) { src = qkv + t * channels + k_at + e; at = e; }
+            else if (e < 2 * dk) { src = qkv + t * channels + q_at + (e - dk); at = e; }
+            else if (e < 2 * dk + cols) { src = qkv + t * channels + v_at + (e - 2 * dk); at = 2 * dk + 2 + (e - 2 * dk); }
+            else if (e == 2 * dk + cols) { src = beta + t * heads + head; at = 2 * dk; }
+            else { src = decay + t * heads + head; at = 2 * dk + 1; }
+            copy4(buf + j * stride + at, src);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (n > 0) fetch(0, stage);
     float s[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        const int r = part + 4 * i;
+        const int r = part + L * i;
         s[i] = (live && r < dk) ? S[(size_t)r * dv + col] : 0.f;
     }
-    const int q_at = g * dk, k_at = kvh * dk + g * dk, v_at = 2 * kvh * dk + head * dv + (live ? col : 0);
-    float kq[BUFS][2 * R], vb[BUFS][3];
-    auto fetch = [&](int t, int buf) {
-        const float* row = qkv + (size_t)t * channels;
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-            const int r = part + 4 * i;
-            kq[buf][i] = r < dk ? row[k_at + r] : 0.f;
-            kq[buf][R + i] = r < dk ? row[q_at + r] : 0.f;
+    const int n_blocks = (n + STAGE_TOKENS - 1) / STAGE_TOKENS;
+    float o_wait = 0.f;                           // the last token's read-out, not reduced over the column's lanes yet
+    int o_token = -1;                             // and its row of `out`
+    for (int block = 0; block < n_blocks; ++block) {
+        float* buf = stage + (block & 1) * STAGE_TOKENS * stride;
+        if (block + 1 < n_blocks) {
+            fetch(block + 1, stage + ((block + 1) & 1) * STAGE_TOKENS * stride);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        vb[buf][0] = row[v_at];
-        vb[buf][1] = beta[(size_t)t * heads + head];
-        vb[buf][2] = decay[(size_t)t * heads + head];
-    };
-    if (n > 0) fetch(first, 0);
-    for (int i0 = 0; i0 < n; i0 += BUFS) {
+        __syncthreads();
+        const int t0 = block * STAGE_TOKENS, count = min(STAGE_TOKENS, n - t0);
+        // A warp issues in order: the read-out's reduction (which nothing of the next token waits for) would hold up the
+        // next token's first instructions, and that token's operands would be asked for only then.  So the operands of
+        // token j + 1 are read before token j's reductions begin, and the read-out of token j - 1 is reduced beside
+        // token j's k . S, shuffle by shuffle.
+        float k[R], q[R], bet, dec, v;
+        auto read = [&](int j, float* kk, float* qq, float& b, float& d, float& vv) {
+            const float* in = buf + j * stride;
+            b = in[2 * dk]; d = in[2 * dk + 1];
+            vv = live ? in[2 * dk + 2 + mine] : 0.f;
 #pragma unroll
-        for (int b = 0; b < BUFS; ++b) {
-            const int i = i0 + b;
-            if (i >= n) break;
-            if (BUFS == 2 && i + 1 < n) fetch(first + i + 1, b ^ 1);
-            const float dec = vb[b][2];
-            float ks = 0.f;
+            for (int i = 0; i < R; ++i) {
+                const int r = part + L * i;
+                kk[i] = r < dk ? in[r] : 0.f;
+                qq[i] = r < dk ? in[dk + r] : 0.f;
+            }
+        };
+        read(0, k, q, bet, dec, v);
+        for (int j = 0; j < count; ++j) {
+            float ks0 = 0.f, ks1 = 0.f;
 #pragma unroll
-            for (int j = 0; j < R; ++j) { s[j] *= dec; ks = fmaf(kq[b][j], s[j], ks); }
-            ks += __shfl_xor_sync(0xffffffffu, ks, 1);
-            ks += __shfl_xor_sync(0xffffffffu, ks, 2);
-            const float u = vb[b][1] * (vb[b][0] - ks);
-            float o = 0.f;
+            for (int i = 0; i < R; ++i) {
+                if (i & 1) ks1 = fmaf(k[i], s[i], ks1); else ks0 = fmaf(k[i], s[i], ks0);
+            }
+            float ks = ks0 + ks1;                 // k . S_old; the decayed state's share is dec times that
+            float kn[R], qn[R], betn = 0.f, decn = 0.f, vn = 0.f;
+            if (j + 1 < count) read(j + 1, kn, qn, betn, decn, vn);
 #pragma unroll
-            for (int j = 0; j < R; ++j) { s[j] = fmaf(kq[b][j], u, s[j]); o = fmaf(kq[b][R + j], s[j], o); }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (live && part == 0) out[((size_t)(first + i) * heads + head) * dv + col] = o;
-            if (BUFS == 1 && i + 1 < n) fetch(first + i + 1, 0);
+            for (int off = 1; off < L; off <<= 1) {
+                ks += __shfl_xor_sync(0xffffffffu, ks, off);
+                o_wait += __shfl_xor_sync(0xffffffffu, o_wait, off);
+            }
+            if (o_token >= 0 && live && part == 0) out[((size_t)o_token * heads + head) * dv + col] = o_wait;
+            const float u = bet * (v - dec * ks);
+            float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                s[i] = fmaf(k[i], u, dec * s[i]);
+                if (i & 1) o1 = fmaf(q[i], s[i], o1); else o0 = fmaf(q[i], s[i], o0);
+            }
+            o_wait = o0 + o1;                     // this lane's share of the read-out: reduced beside the next token's k . S
+            o_token = first + t0 + j;
+#pragma unroll
+            for (int i = 0; i < R; ++i) { k[i] = kn[i]; q[i] = qn[i]; }
+            bet = betn; dec = decn; v = vn;
         }
+        __syncthreads();                          // the block after next is fetched into this buffer
     }
 #pragma unroll
+    for (int off = 1; off < L; off <<= 1) o_wait += __shfl_xor_sync(0xffffffffu, o_wait, off);
+    if (o_token >= 0 && live && part == 0) out[((size_t)o_token * heads + head) * dv + col] = o_wait;
+#pragma unroll
     for (int i = 0; i < R; ++i) {
-        const int r = part + 4 * i;
+        const int r = part + L * i;
         if (live && r < dk) S[(size_t)r * dv + col] = s[i];
     }
 }
@@ -214,17 +275,59 @@ CISR_EXPORT int cisr_delta_max_key_dim() { return 256; }
 
 CISR_EXPORT int cisr_delta_recurrence(const float* qkv, const float* beta, const float* decay, float* state, long long state_stride,
                                       const int* req_slot, const int* q_start, const int* q_len, float* out, int heads, int kvh,
-                                      int dk, int dv, int n_req, void* stream) {
+                                      int dk, int dv, int n_req, int lanes_per_column, void* stream) {
     if (n_req <= 0) return 0;
     if (dk <= 0 || dk > 256 || dv <= 0 || heads % kvh) return -2;
-    const dim3 grid(n_req, heads, (dv + 7) / 8);
     cudaStream_t s = (cudaStream_t)stream;
-#define CISR_DELTA(R, B) return launch_kernel(delta_recurrence_kernel<R, B>, grid, dim3(32), 0, s, g_pdl, qkv, beta, decay, state, state_stride, \
-                                           req_slot, q_start, q_len, out, heads, kvh, dk, dv)
-    if (dk <= 32) CISR_DELTA(8, 2);
-    if (dk <= 64) CISR_DELTA(16, 2);
-    if (dk <= 128) CISR_DELTA(32, 2);
-    CISR_DELTA(64, 1);
+    // + 256 floats: a lane's row index runs past a short key head's end; such reads are discarded but must stay inside
+    const auto smem_for = [dk](int lanes) { return sizeof(float) * (2 * STAGE_TOKENS * (size_t)stage_stride(dk, DELTA_THREADS / lanes) + 256); };
+    static int sms = 0;
+    if (!sms) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 148;
+    }
+    // lanes per column: the fewest that give the launch about four warps per SM (or all 32)
+    int lanes = 8;
+    while (lanes < 32 && (long long)n_req * heads * ((dv * lanes + DELTA_THREADS - 1) / DELTA_THREADS) < sms) lanes *= 2;
+    if (lanes_per_column) {                          // the caller's choice (tests)
+        if (lanes_per_column != 4 && lanes_per_column != 8 && lanes_per_column != 16 && lanes_per_column != 32) return -2;
+        lanes = lanes_per_column;
+    }
+    while (lanes < 32 && dk > lanes * 64) lanes *= 2;
+#define CISR_DELTA(R, L)                                                                                                  \
+    do {                                                                                                                  \
+        const size_t smem = smem_for(L);                                                                                  \
+        static size_t configured = 48 * 1024;                                                                             \
+        if (smem > configured) {                                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(delta_recurrence_kernel<R, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e;                                                                          \
+            configured = smem;                                                                                            \
+        }                                                                                                                 \
+        return launch_kernel(delta_recurrence_kernel<R, L>, dim3(n_req, heads, (dv * L + DELTA_THREADS - 1) / DELTA_THREADS), dim3(DELTA_THREADS), smem, s, g_pdl, \
+                             qkv, beta, decay, state, state_stride, req_slot, q_start, q_len, out, heads, kvh, dk, dv);   \
+    } while (0)
+    const int rows = (dk + lanes - 1) / lanes;       // per lane
+    if (lanes == 4) {
+        if (rows <= 8) CISR_DELTA(8, 4);
+        if (rows <= 16) CISR_DELTA(16, 4);
+        if (rows <= 32) CISR_DELTA(32, 4);
+        CISR_DELTA(64, 4);
+    }
+    if (lanes == 8) {
+        if (rows <= 4) CISR_DELTA(4, 8);
+        if (rows <= 8) CISR_DELTA(8, 8);
+        if (rows <= 16) CISR_DELTA(16, 8);
+        CISR_DELTA(32, 8);
+    }
+    if (lanes == 16) {
+        if (rows <= 2) CISR_DELTA(2, 16);
+        if (rows <= 4) CISR_DELTA(4, 16);
+        if (rows <= 8) CISR_DELTA(8, 16);
+        CISR_DELTA(16, 16);
+    }
+    if (rows <= 2) CISR_DELTA(2, 32);
+    if (rows <= 4) CISR_DELTA(4, 32);
+    CISR_DELTA(8, 32);
 #undef CISR_DELTA
 }
 

@@ -647,10 +647,11 @@ def delta_keep(proj, state, req_slot, q_start, q_len, n_req, taps, channels, mat
                                     _p(req_slot), _p(q_start), _p(q_len), taps, channels, n_req, _stream()), "delta_keep")
 
 
-def delta_recurrence(qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim) -> None:
-    """The state's walk over each request's tokens, in order; o [tokens, heads, value_dim] float."""
+def delta_recurrence(qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim, lanes=0) -> None:
+    """The state's walk over each request's tokens, in order; o [tokens, heads, value_dim] float.  `lanes`: how many lanes
+    share a column of the state (4, 8, 16 or 32); 0: chosen by the size of the launch."""
     _check(_delta().cisr_delta_recurrence(_p(qkv), _p(beta), _p(decay), _p(state), ctypes.c_longlong(state.shape[1]), _p(req_slot),
-                                          _p(q_start), _p(q_len), _p(o), heads, kv_heads, key_dim, value_dim, n_req, _stream()),
+                                          _p(q_start), _p(q_len), _p(o), heads, kv_heads, key_dim, value_dim, n_req, int(lanes), _stream()),
            "delta_recurrence")
 
 
@@ -662,7 +663,8 @@ def delta_output(o, proj, gate_col, norm_w, eps, out, heads, value_dim) -> None:
 
 def delta_step(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
                norm_w: torch.Tensor, eps: float, norm_eps: float, token_req: torch.Tensor, req_slot: torch.Tensor, q_start: torch.Tensor,
-               q_len: torch.Tensor, n_req: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, out: torch.Tensor) -> torch.Tensor:
+               q_len: torch.Tensor, n_req: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, out: torch.Tensor,
+               lanes: int = 0) -> torch.Tensor:
     """The gated delta rule for a step's tokens (see csrc/delta.cu).  proj float [tokens, cols]: the stacked projection
     q | k | v | gate | b | a (cols may be padded beyond them); conv_w float [2 * kv_heads * key_dim + heads * value_dim, taps];
     state float [slots, heads * key_dim * value_dim + (taps - 1) * conv channels] is read and advanced for the step's
@@ -689,7 +691,7 @@ def delta_step(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch
                   value_dim, norm_eps)
     if taps > 1:
         delta_keep(proj, state, req_slot, q_start, q_len, n_req, taps, channels, matrix)
-    delta_recurrence(qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim)
+    delta_recurrence(qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim, lanes)
     delta_output(o, proj, channels, norm_w, eps, out, heads, value_dim)
     return out
 
@@ -1419,7 +1421,7 @@ _DESCRIBE = {
     "activation": lambda x, out, kind: (int(x.shape[0]), int(x.shape[1])),
     "delta_prepare": lambda proj, conv_w, taps, *a: (int(proj.shape[0]), int(conv_w.shape[0]), int(taps)),
     "delta_keep": lambda proj, state, req_slot, q_start, q_len, n_req, taps, channels, matrix: (int(n_req), int(channels), int(taps)),
-    "delta_recurrence": lambda qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim:
+    "delta_recurrence": lambda qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim, lanes=0:
         (int(qkv.shape[0]), int(n_req), int(heads), int(kv_heads), int(key_dim), int(value_dim)),
     "delta_output": lambda o, proj, *a: (int(o.shape[0]), int(o.shape[1] * o.shape[2])),
     "rope_store": lambda proj, *rest, **kw: (int(proj.shape[0]), int(proj.shape[1])),

@@ -85,6 +85,7 @@ class DenseMLP(FeedForward):
         self.names = dict({"up": "up", "down": "down"}, **dict(spec.get("names", {})))
         self.up = None
         self.down = None
+        self._groups = {}
 
     def tensor_needs(self) -> Dict[str, TensorNeed]:
         return {self.names["up"]: TensorNeed((self.inter, self.hidden)),
@@ -98,8 +99,28 @@ class DenseMLP(FeedForward):
         return ([("elementwise.cu", {}, ())] + kernels.gemm_jobs(self.dtype)
                 + (kernels.skinny_jobs() if self.dtype == torch.bfloat16 else []))
 
+    def _single_group(self, tiles: int, device) -> torch.Tensor:
+        """Tile -> weight block list of the grouped tensor-core product, for one block: all zeros."""
+        groups = self._groups.get(tiles)
+        if groups is None:
+            groups = self._groups[tiles] = torch.zeros(tiles, dtype=torch.int32, device=device)
+        return groups
+
     def forward(self, h, ctx):
         h = as_tensor(h)
-        act = torch.empty((h.shape[0], self.down.shape[1]), dtype=self.dtype, device=h.device)
+        tokens = h.shape[0]
+        if (self.activation == "relu_squared" and self.down.shape[1] == self.inter and kernels.tcgen05_ok(h, self.up)):
+            # many tokens: the squared relu is the epilogue of the first product (the grouped tcgen05 product with one
+            # group, which takes whole 128-row tiles: the last tile is filled up with zero rows)
+            rows = -(-tokens // kernels.MOE_TILE) * kernels.MOE_TILE
+            if rows != tokens:
+                padded = torch.zeros((rows, self.hidden), dtype=self.dtype, device=h.device)
+                padded[:tokens].copy_(h)
+                h = padded
+            act = torch.empty((rows, self.inter), dtype=self.dtype, device=h.device)
+            kernels.gemm_tcgen05_grouped(h, self.up.view(1, self.inter, self.hidden), act, self._single_group(rows // kernels.MOE_TILE, h.device),
+                                         rows_in_use=tokens)
+            return linear(act[:tokens], self.down)
+        act = torch.empty((tokens, self.down.shape[1]), dtype=self.dtype, device=h.device)
         kernels.activation(linear(h, self.up), act, self.activation)
         return linear(act, self.down)

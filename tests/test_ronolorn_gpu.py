@@ -179,12 +179,14 @@ def test_attention_rows_kernel(dtype, from_keys, norm, interleaved, key_dim, val
     assert int((kc != 0).any(-1).sum()) == T * hkv, "rows of other pages and offsets were touched"
 
 
+@pytest.mark.parametrize("lanes", [0, 4, 8, 16, 32])
 @pytest.mark.parametrize("heads, kvh, dk, dv, taps", [(4, 2, 20, 24, 3), (2, 1, 32, 64, 4), (3, 3, 72, 40, 1), (1, 1, 130, 9, 2),
-                                                       (2, 2, 128, 16, 5), (2, 1, 200, 8, 2)])
-def test_delta_kernels_carry_their_state_across_portions(heads, kvh, dk, dv, taps):
+                                                       (2, 2, 128, 16, 5), (2, 1, 200, 8, 2), (1, 1, 256, 3, 2)])
+def test_delta_kernels_carry_their_state_across_portions(heads, kvh, dk, dv, taps, lanes):
     """The recurrence, the convolution with kept inputs, decay, beta, unit norms and the gated output norm against the
     plain mixer on whole sequences; two requests side by side in portions down to one token (shorter than the taps),
-    one of them in a slot that held another request's state before."""
+    one of them in a slot that held another request's state before; with every number of lanes per column of the state
+    that the recurrence kernel can be launched with (0: its own choice)."""
     from cisr_b200.ops import kernels
     hidden, eps = 48, 1e-5
     g = torch.Generator().manual_seed(dk * 7 + dv)
@@ -220,7 +222,8 @@ def test_delta_kernels_carry_their_state_across_portions(heads, kvh, dk, dv, tap
         out = torch.empty((rows.shape[0], heads * dv), dtype=torch.float32, device="cuda")
         dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).cuda()
         kernels.delta_step(proj, conv, taps, state, W["A_log"].cuda(), W["dt_bias"].cuda(), W["norm"].cuda(), eps, 1e-6,
-                           dev(token_req), dev([slot[r] for r in batch]), dev(q_start), dev(sizes), len(batch), heads, kvh, dk, dv, out)
+                           dev(token_req), dev([slot[r] for r in batch]), dev(q_start), dev(sizes), len(batch), heads, kvh, dk, dv, out,
+                           lanes=lanes)
         for i, (r, n) in enumerate(zip(batch, sizes)):
             got[r].append(out[q_start[i]:q_start[i] + n].cpu())
             at[r] += n
