@@ -34,7 +34,7 @@ __device__ __forceinline__ float turned(const float* head, const float* w, float
 }
 
 template <typename QT, typename CT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 attention_rows_kernel(const float* __restrict__ proj, int row_stride, int k_col, int v_col, const float* __restrict__ bias,
                       const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_half, int interleaved,
@@ -117,7 +117,9 @@ CISR_EXPORT int cisr_attention_rows(const float* proj, int row_stride, int k_col
             if (e != cudaSuccess) return (int)e;                                                                          \
             configured = smem;                                                                                            \
         }                                                                                                                 \
-        return launch_kernel(attention_rows_kernel<QT, CT>, dim3(tokens), dim3(256), smem, s, g_pdl, proj, row_stride, k_col, v_col, bias, \
+        /* few tokens (a decode step): a token's row on four times the threads */                                        \
+        const int threads = (tokens <= 64 && n_cols >= 1024) ? 1024 : 256;                                                \
+        return launch_kernel(attention_rows_kernel<QT, CT>, dim3(tokens), dim3(threads), smem, s, g_pdl, proj, row_stride, k_col, v_col, bias, \
                              q_norm, k_norm, eps, cos_t, sin_t, rot_half, interleaved, (QT*)q_out, (CT*)k_cache, (CT*)v_cache,   \
                              token_req, positions, req_slot, block_table, table_width, page_size, hq, hkv, key_dim, value_dim, D, n_cols); \
     } while (0)

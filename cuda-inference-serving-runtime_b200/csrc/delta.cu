@@ -30,7 +30,7 @@ __device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // conv channels: [q: kvh * dk][k: kvh * dk][v: heads * dv]; proj columns: the same, then gate [heads * dv], b [heads], a [heads]
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 delta_prepare_kernel(const float* __restrict__ proj, int row_stride, const float* __restrict__ conv_w, int taps,
                      const float* __restrict__ state, long long state_stride, long long keep_offset,
                      const float* __restrict__ a_log, const float* __restrict__ dt_bias,
@@ -257,7 +257,8 @@ CISR_EXPORT int cisr_delta_prepare(const float* proj, int row_stride, const floa
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    return launch_kernel(delta_prepare_kernel, dim3(tokens), dim3(256), smem, (cudaStream_t)stream, g_pdl, proj, row_stride, conv_w, taps,
+    const int threads = (tokens <= 64 && channels >= 1024) ? 1024 : 256;      // few tokens (a decode step): a token's channels on more threads
+    return launch_kernel(delta_prepare_kernel, dim3(tokens), dim3(threads), smem, (cudaStream_t)stream, g_pdl, proj, row_stride, conv_w, taps,
                          state, state_stride, keep_offset, a_log, dt_bias, token_req, req_slot, q_start, qkv, beta, decay, heads, kvh,
                          dk, dv, norm_eps);
 }

@@ -27,7 +27,7 @@ constexpr int MAX_STREAMS = 16;
 
 // MS: the most streams this instance holds in registers (4, 8 or 16)
 template <typename WT, typename OT, int MS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(MS == 4 ? 1024 : 256)
 hyper_mix_norm_kernel(const float* __restrict__ source, long long source_stride, float* __restrict__ streams,
                       const float* __restrict__ y, const float* __restrict__ bias, const float* __restrict__ mix,
                       const float* __restrict__ out_w, const float* __restrict__ in_w, const WT* __restrict__ norm_w,
@@ -124,7 +124,9 @@ CISR_EXPORT int cisr_hyper_mix_norm(const float* source, int source_is_row, floa
             if (e != cudaSuccess) return (int)e;                                                                        \
             configured = smem;                                                                                          \
         }                                                                                                               \
-        return launch_kernel(hyper_mix_norm_kernel<WT, OT, MS>, dim3(n_rows), dim3(256), smem, s, g_pdl, source, stride, streams, y, bias, \
+        /* few rows (a decode step): the row's channels on four times the threads, so that its loads are in flight together */ \
+        const int threads = (MS == 4 && n_rows <= 64 && hidden >= 1024) ? 1024 : 256;                                   \
+        return launch_kernel(hyper_mix_norm_kernel<WT, OT, MS>, dim3(n_rows), dim3(threads), smem, s, g_pdl, source, stride, streams, y, bias, \
                              mix, out_w, in_w, (const WT*)norm_w, (OT*)h, rows, n_streams, hidden, eps, kind, store);   \
     } while (0)
 #define CISR_HYPER(WT, OT)                                                 \

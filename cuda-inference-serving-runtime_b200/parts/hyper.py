@@ -109,6 +109,8 @@ class HyperConnectionBlock:
         self.dtype = dtype
         self.mixer_norm = build_part(NORMS, spec.mixer_norm, dtype, "norm")
         self.mixer = build_part(MIXERS, spec.mixer, dtype, "mixer")
+        if getattr(self.mixer, "defers_output_bias", False):
+            self.mixer.bias_taken_by_arrangement = True
         self.mixer_hyper = HyperWeights(spec.extras["mixer_hyper"], dtype) if "mixer_hyper" in spec.extras else None
         self.feed_forward = self.feed_forward_norm = self.feed_forward_hyper = None
         if spec.feed_forward is not None:
@@ -130,7 +132,7 @@ class HyperConnectionBlock:
     def forward(self, stream: HyperStream, ctx, cache) -> None:
         h = stream.read(self.mixer_hyper, self.mixer_norm, self.dtype)
         y = self.mixer.forward(h, ctx, cache)
-        bias = self.mixer.output_bias if getattr(self.mixer, "defers_output_bias", False) else None
+        bias = self.mixer.output_bias if getattr(self.mixer, "bias_taken_by_arrangement", False) else None
         stream.write(y, self.mixer_hyper, bias)
         if self.feed_forward is not None:
             h = stream.read(self.feed_forward_hyper, self.feed_forward_norm, self.dtype)

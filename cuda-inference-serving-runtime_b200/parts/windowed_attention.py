@@ -36,7 +36,9 @@ class WindowedAttention(Mixer):
     bias (the set of projections that have one, among "q", "k", "v", "o"), names."""
 
     graph_safe = True
-    defers_output_bias = True       # the arrangement adds `output_bias` where it adds the output to the stream
+    # An arrangement that adds the mixer's output to the stream in a kernel of its own may add `output_bias` there: it sets
+    # `bias_taken_by_arrangement` when it is built.  Otherwise the mixer adds the bias itself.
+    defers_output_bias = True
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
@@ -64,6 +66,7 @@ class WindowedAttention(Mixer):
         if getattr(self.position, "dim", 0) > self.key_dim:
             raise ValueError("the position encoding turns more coordinates than a key head has")
         self.w_in = self.o = self.in_bias = self.output_bias = self.q_norm = self.k_norm = None
+        self.bias_taken_by_arrangement = False
 
     # ---------------------------------------------------------------- tensors
     def tensor_needs(self) -> Dict[str, TensorNeed]:
@@ -135,4 +138,7 @@ class WindowedAttention(Mixer):
                                key_dim=self.key_dim, value_dim=self.value_dim)
         mixed = paged_attention(ctx.plan_for(self), q, cache.k, cache.v, cache, ctx, self.hq, self.hkv, self.scale, self.window,
                                 sink=self.sink)
-        return linear(mixed.view(tokens, self.hq * self.width), self.o)
+        y = linear(mixed.view(tokens, self.hq * self.width), self.o)
+        if self.output_bias is not None and not self.bias_taken_by_arrangement:
+            kernels.bias_add(y, self.output_bias)
+        return y

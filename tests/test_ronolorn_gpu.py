@@ -177,6 +177,10 @@ def test_attention_rows_kernel(dtype, from_keys, norm, interleaved, key_dim, val
         assert (got_k[:, :key_dim] - k[t]).abs().max() < tol * k.abs().max() and (got_k[:, key_dim:] == 0).all()
         assert (got_v[:, :value_dim] - v[t]).abs().max() < tol * v.abs().max() and (got_v[:, value_dim:] == 0).all()
     assert int((kc != 0).any(-1).sum()) == T * hkv, "rows of other pages and offsets were touched"
+    # the output bias, where no arrangement takes it into its own kernel
+    y = torch.randn(T, 24, generator=g).cuda()
+    b = torch.randn(24, generator=g).cuda()
+    assert torch.equal(kernels.bias_add(y.clone(), b), y + b)
 
 
 @pytest.mark.parametrize("lanes", [0, 4, 8, 16, 32])
@@ -307,6 +311,22 @@ def test_unequal_requests_side_by_side_with_pages_and_slots_used_again(case, dty
     assert not stepper.cache.requests and len(stepper.cache.free_slots) == 4
     assert all(g.pool.n_free == g.pool.n_pages for g in stepper.cache.page_groups)
     assert any(g.pool.taken > g.pool.n_pages for g in stepper.cache.page_groups), "no page was used twice"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_are_no_multiples_of_eight(dtype, tmp_path):
+    """Width, feed-forward width, head widths and vocabulary that fit no 16-byte group: the products take the paths
+    that have no alignment to rely on, the padded operands stay zero where they are padding."""
+    cfg = {"architecture": "Ronolorn", "vocab": 83, "width": 100, "embedding": {"scale": 3.0}, "norm": {"eps": 1e-5}, "streams": 5,
+           "layers": [rm.layer("attention", rm.attention(3, 1, 10, 6, 0.3, window=21, rot={"base": 900.0, "dims": 6}), 50),
+                      rm.layer("delta", rm.delta(3, 1, 7, 5, 2), 33),
+                      rm.layer("attention_2", rm.attention(2, 2, 18, 18, 0.2, window=9, rot={"base": 5000.0, "dims": 18, "scaling": rm.YARN}), 27)]}
+    weights = rm.make_weights(cfg, 77)
+    model = model_of(cfg, weights, tmp_path, dtype)
+    requests = {"u": rm.random_tokens(cfg, 140, 1), "v": rm.random_tokens(cfg, 37, 2)}
+    reference = {k: plain(cfg, weights, t) for k, t in requests.items()}
+    for steps in (replay.trace_whole(requests), replay.trace_mixed(requests, seed=2, max_live=2), replay.trace_portions(requests, (2, 15, 1))):
+        compare(replay.run_steps(stepper_for(model, steps, slack_pages=2), steps), requests, reference, dtype, scale=4.0)
 
 
 def test_a_request_alone_and_in_a_crowd(tmp_path_factory):
