@@ -455,7 +455,7 @@ def ronolorn_pair(width: int, layers: int, heads: int, ff_active: int, experts: 
     kv = max(1, heads // 4)
     rot = {"base": 10000.0, "dims": 64}
     att = {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024}, "rot": rot}
-    att2 = dict(att, kv_heads=1, rot=dict(rot, scaling={"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}))
+    att2 = dict(att, kv_heads=1, rot=dict(rot, scaling={"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 2.0}))
     delta = {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 64, "conv": 4}
     order = [("attention", att), ("attention_2", att2), ("delta", delta), ("attention", att)]
     mlp = {"kind": "dense", "ff": ff_active * 3 // 2}

@@ -33,6 +33,20 @@ __device__ __forceinline__ float turned(const float* head, const float* w, float
     return v;
 }
 
+// Coordinates d and d + 1 (d even) of a head after norm and rotation.  Neighbouring pairs turn together, so one pair of
+// table entries serves both; the other pairing takes each coordinate's partner from across the head.
+__device__ __forceinline__ float2 turned_pair(const float* head, const float* w, float inv, int d, int width, int rot_half,
+                                              int interleaved, const float* cs, const float* sn) {
+    if (d + 1 >= width || !interleaved || d >= 2 * rot_half)
+        return make_float2(d < width ? turned(head, w, inv, d, rot_half, interleaved, cs, sn) : 0.f,
+                           d + 1 < width ? turned(head, w, inv, d + 1, rot_half, interleaved, cs, sn) : 0.f);
+    const float a = head[d] * inv * (w ? w[d] : 1.f), b = head[d + 1] * inv * (w ? w[d + 1] : 1.f);
+    const float c = cs[d >> 1], s = sn[d >> 1];
+    return make_float2(a * c - b * s, b * c + a * s);
+}
+__device__ __forceinline__ void store_pair(float* dst, float2 v) { *reinterpret_cast<float2*>(dst) = v; }
+__device__ __forceinline__ void store_pair(__nv_bfloat16* dst, float2 v) { *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v.x, v.y); }
+
 template <typename QT, typename CT>
 __global__ void __launch_bounds__(1024)
 attention_rows_kernel(const float* __restrict__ proj, int row_stride, int k_col, int v_col, const float* __restrict__ bias,
@@ -66,25 +80,24 @@ attention_rows_kernel(const float* __restrict__ proj, int row_stride, int k_col,
     }
     const float* cs = cos_t ? cos_t + (size_t)t * rot_half : nullptr;
     const float* sn = sin_t ? sin_t + (size_t)t * rot_half : nullptr;
-    for (int i = threadIdx.x; i < hq * D; i += blockDim.x) {
-        const int h = i / D, d = i - h * D;
-        float v = 0.f;
-        if (d < key_dim) v = turned(row + h * key_dim, q_norm ? q_norm + h * key_dim : nullptr, inv_q, d, rot_half, interleaved, cs, sn);
-        q_out[((size_t)t * hq + h) * D + d] = from_float<QT>(v);
-    }
+    // a warp per head, a lane per pair of neighbouring coordinates (D is even: pairs never straddle heads)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int h = warp; h < hq; h += n_warps)
+        for (int d = 2 * lane; d < D; d += 64)
+            store_pair(q_out + ((size_t)t * hq + h) * D + d,
+                       turned_pair(row + h * key_dim, q_norm ? q_norm + h * key_dim : nullptr, inv_q, d, key_dim, rot_half, interleaved, cs, sn));
     if (!k_cache) return;
     const int page = block_table[(size_t)slot * table_width + pos / page_size];
     if (page < 0) return;                     // the host reserves a page before every write; never follow a missing entry
     const int off = pos % page_size;
-    for (int i = threadIdx.x; i < hkv * D; i += blockDim.x) {
-        const int g = i / D, d = i - g * D;
-        float kv = 0.f, vv = 0.f;
-        if (d < key_dim) kv = turned(row + k_col + g * key_dim, k_norm ? k_norm + g * key_dim : nullptr, inv_k, d, rot_half, interleaved, cs, sn);
-        if (d < value_dim) vv = v_col >= 0 ? row[v_col + g * value_dim + d] : row[k_col + g * key_dim + d];
-        const size_t dst = (((size_t)page * hkv + g) * page_size + off) * D + d;
-        k_cache[dst] = from_float<CT>(kv);
-        v_cache[dst] = from_float<CT>(vv);
-    }
+    for (int g = warp; g < hkv; g += n_warps)
+        for (int d = 2 * lane; d < D; d += 64) {
+            const float* vs = v_col >= 0 ? row + v_col + g * value_dim : row + k_col + g * key_dim;
+            const size_t dst = (((size_t)page * hkv + g) * page_size + off) * D + d;
+            store_pair(k_cache + dst, turned_pair(row + k_col + g * key_dim, k_norm ? k_norm + g * key_dim : nullptr, inv_k, d, key_dim,
+                                                  rot_half, interleaved, cs, sn));
+            store_pair(v_cache + dst, make_float2(d < value_dim ? vs[d] : 0.f, d + 1 < value_dim ? vs[d + 1] : 0.f));
+        }
 }
 
 // out[t][c] += bias[c]
