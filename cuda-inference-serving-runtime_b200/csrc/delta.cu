@@ -101,6 +101,10 @@ constexpr int STAGE_TOKENS = 16;
 constexpr int DELTA_THREADS = 256;            // eight warps share the staged tokens; a CTA owns 256 / L columns of one head
 __host__ __device__ inline int stage_stride(int dk, int columns) { return 2 * dk + 2 + columns; }
 
+__device__ __forceinline__ void copy16(float* dst, const float* src) {      // both 16-byte aligned
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copies_done() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void copy4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
@@ -110,7 +114,7 @@ __global__ void __launch_bounds__(DELTA_THREADS)
 delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
                         float* __restrict__ state, long long state_stride, const int* __restrict__ req_slot,
                         const int* __restrict__ q_start, const int* __restrict__ q_len, float* __restrict__ out,
-                        int heads, int kvh, int dk, int dv) {
+                        int heads, int kvh, int dk, int dv, int below) {
     extern __shared__ float stage[];          // [2][STAGE_TOKENS][stage_stride(dk, columns of the CTA)]
     pdl_trigger();
     constexpr int CPC = DELTA_THREADS / L;    // columns per CTA
@@ -125,7 +129,8 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
     const int stride = stage_stride(dk, CPC), cols = min(CPC, dv - col0);
     const int q_at = g * dk, k_at = kvh * dk + g * dk, v_at = 2 * kvh * dk + head * dv + col0;
     const int per_token = 2 * dk + cols + 2;  // floats a token brings: k, q, the CTA's columns of v, beta, decay
-    pdl_wait();
+    pdl_wait();                               // also where nothing is left to do: the kernel after this one relies on the chain of waits
+    if (below > 0 && n >= below) return;      // a portion that long is the chunk kernels'
     auto fetch = [&](int block, float* buf) {          // tokens [block * STAGE_TOKENS, ...) of the portion, by all threads
         const int t0 = block * STAGE_TOKENS, count = min(STAGE_TOKENS, n - t0);
         for (int i = tid; i < count * per_token; i += DELTA_THREADS) {
@@ -219,6 +224,240 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
     }
 }
 
+// ------------------------------------------------------------------ the same recurrence, a chunk of tokens at a time
+// For the C tokens of a chunk with the state S0 before it, c_t the product of the decays up to token t inside the chunk:
+//     S_t = c_t S0 + sum_{i<=t} (c_t / c_i) k_i u_i^T,      u_t + sum_{i<t} A[t][i] u_i = beta_t (v_t - c_t S0^T k_t),
+//     A[t][i] = beta_t (c_t / c_i) (k_t . k_i)              (i < t)
+// so with T = (I + A)^-1 (lower triangular, ones on the diagonal) and P[t][i] = (c_t / c_i) (q_t . k_i) (i <= t):
+//     U = T B,   B[t] = beta_t (v_t - c_t (K S0)[t]);   O[t] = c_t (Q S0)[t] + (P U)[t];   S_C = c_C S0 + sum_i (c_C / c_i) k_i u_i^T.
+// T and P depend on no state: `delta_chunk_tables` makes them for every chunk of the step at once, a CTA per (chunk, head).
+// `delta_chunk_walk` then carries the state from chunk to chunk, a CTA per (request, head, CHUNK_COLS value columns), with
+// small matrix products in shared memory instead of a chain of shuffles per token.  Ratios of decays are taken as
+// exp(l_t - l_i) from sums of logarithms (t >= i: never above one; a decay of zero is floored at e^-80).  Float throughout.
+constexpr int CHUNK = 64, CHUNK_COLS = 16, CHUNK_THREADS = 256;
+__host__ __device__ inline int chunk_row_stride(int dk) { return dk % 4 == 0 ? dk + 4 : dk + 1; }
+
+__global__ void __launch_bounds__(CHUNK_THREADS)
+delta_chunk_tables_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
+                          const int* __restrict__ chunk_req, const int* __restrict__ chunk_t0, const int* __restrict__ q_start,
+                          const int* __restrict__ q_len, float* __restrict__ tables, int heads, int kvh, int dk, int dv) {
+    extern __shared__ float sm[];
+    const int ld = dk + 1, lc_ = CHUNK + 1;
+    float* Ks = sm;                           // [CHUNK][dk + 1]
+    float* Qs = Ks + CHUNK * ld;              // [CHUNK][dk + 1]
+    float* As = Qs + CHUNK * ld;              // [CHUNK][CHUNK + 1]
+    float* Ts = As + CHUNK * lc_;             // [CHUNK][CHUNK + 1]
+    float* lg = Ts + CHUNK * lc_;             // [CHUNK] sums of log decays
+    float* bt = lg + CHUNK;                   // [CHUNK] beta
+    pdl_trigger();
+    const int chunk = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const int req = chunk_req[chunk], t0 = chunk_t0[chunk];
+    const int count = min(CHUNK, q_len[req] - t0), first = q_start[req] + t0;
+    const int g = head / (heads / kvh), channels = 2 * kvh * dk + heads * dv;
+    pdl_wait();
+    {
+        const int t = tid >> 2;
+        const float* row = qkv + (size_t)(first + t) * channels;
+        for (int r = tid & 3; r < dk; r += 4) {
+            Ks[t * ld + r] = t < count ? row[kvh * dk + g * dk + r] : 0.f;
+            Qs[t * ld + r] = t < count ? row[g * dk + r] : 0.f;
+        }
+    }
+    if (tid < CHUNK) {
+        bt[tid] = tid < count ? beta[(size_t)(first + tid) * heads + head] : 0.f;
+        lg[tid] = tid < count ? fmaxf(logf(decay[(size_t)(first + tid) * heads + head]), -80.f) : 0.f;
+    }
+    __syncthreads();
+    if (tid == 0) {                           // the running sum, in token order
+        float sum = 0.f;
+        for (int t = 0; t < CHUNK; ++t) { sum += lg[t]; lg[t] = sum; }
+    }
+    __syncthreads();
+    // 16 entries of row t per thread: A below the diagonal, P on and below it
+    float* out_T = tables + ((size_t)chunk * heads + head) * (2 * CHUNK * CHUNK + CHUNK);
+    float* out_P = out_T + CHUNK * CHUNK;
+    {
+        const int t = tid >> 2, i0 = (tid & 3) * 16;
+        float kk[16], qk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { kk[j] = 0.f; qk[j] = 0.f; }
+#pragma unroll 2
+        for (int r = 0; r < dk; ++r) {
+            const float kt = Ks[t * ld + r], qt = Qs[t * ld + r];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float ki = Ks[(i0 + j) * ld + r];
+                kk[j] = fmaf(kt, ki, kk[j]);
+                qk[j] = fmaf(qt, ki, qk[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int i = i0 + j;
+            const float ratio = i <= t ? expf(lg[t] - lg[i]) : 0.f;
+            As[t * lc_ + i] = i < t ? bt[t] * ratio * kk[j] : 0.f;
+            out_P[t * CHUNK + i] = ratio * qk[j];
+        }
+    }
+    if (tid < CHUNK) out_T[2 * CHUNK * CHUNK + tid] = lg[tid];
+    __syncthreads();
+    // T = (I + A)^-1 by forward substitution: T[t][c] = [t == c] - sum_{c <= i < t} A[t][i] T[i][c].  Four neighbouring
+    // lanes own column c and take every fourth i; a row is finished by two shuffles before the next row reads it.
+    {
+        const int c = tid >> 2, p = tid & 3;
+        for (int t = 0; t < CHUNK; ++t) {
+            float a = 0.f;
+#pragma unroll 4
+            for (int i = c + p; i < t; i += 4) a = fmaf(-As[t * lc_ + i], Ts[i * lc_ + c], a);
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            a += __shfl_xor_sync(0xffffffffu, a, 2);
+            if (p == 0) Ts[t * lc_ + c] = t < c ? 0.f : (t == c ? 1.f : 0.f) + a;
+            __syncwarp();
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < CHUNK * CHUNK; i += CHUNK_THREADS) out_T[i] = Ts[(i / CHUNK) * lc_ + (i % CHUNK)];
+}
+
+__global__ void __launch_bounds__(CHUNK_THREADS)
+delta_chunk_walk_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ tables,
+                        const int* __restrict__ req_chunk0, float* __restrict__ state, long long state_stride,
+                        const int* __restrict__ req_slot, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                        float* __restrict__ out, int heads, int kvh, int dk, int dv, int least) {
+    extern __shared__ __align__(16) float sm[];
+    // Row strides that are multiples of 4 (16-byte rows for vector copies) and 4 mod 32 (rows t, t + 1, ... of a warp's
+    // eight fall into different banks); odd key widths keep scalar copies and a stride of dk + 1.
+    const bool vec = dk % 4 == 0 && dv % 4 == 0;
+    const int ld = chunk_row_stride(dk), lc_ = CHUNK + 4;
+    float* Ks = sm;                           // [CHUNK][ld]
+    float* Qs = Ks + CHUNK * ld;              // [CHUNK][ld]
+    float* Ts = Qs + CHUNK * ld;              // [CHUNK][CHUNK + 4]
+    float* Ps = Ts + CHUNK * lc_;             // [CHUNK][CHUNK + 4]
+    float* S0 = Ps + CHUNK * lc_;             // [dk][CHUNK_COLS]
+    float* Bs = S0 + dk * CHUNK_COLS;         // [CHUNK][CHUNK_COLS]: B, then U
+    float* Vs = Bs + CHUNK * CHUNK_COLS;      // [CHUNK][CHUNK_COLS]
+    float* lg = Vs + CHUNK * CHUNK_COLS;      // [CHUNK]
+    float* bt = lg + CHUNK;                   // [CHUNK]
+    float* wl = bt + CHUNK;                   // [CHUNK]: c_C / c_i
+    pdl_trigger();
+    const int req = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const int n = q_len[req];
+    const int col0 = blockIdx.z * CHUNK_COLS, cols = min(CHUNK_COLS, dv - col0);
+    const int g = head / (heads / kvh), channels = 2 * kvh * dk + heads * dv;
+    const int first = q_start[req];
+    float* S = state + (size_t)req_slot[req] * state_stride + (size_t)head * dk * dv;
+    pdl_wait();
+    if (n < least) return;                    // short portions and single tokens are the token-by-token kernel's
+    for (int i = tid; i < dk * CHUNK_COLS; i += CHUNK_THREADS) {
+        const int r = i / CHUNK_COLS, j = i - r * CHUNK_COLS;
+        S0[i] = j < cols ? S[(size_t)r * dv + col0 + j] : 0.f;
+    }
+    const int t = tid >> 2, j0 = (tid & 3) * 4;        // this thread's four entries of every [CHUNK][CHUNK_COLS] product
+    const int n_chunks = (n + CHUNK - 1) / CHUNK;
+    for (int c = 0; c < n_chunks; ++c) {
+        const int t0 = c * CHUNK, count = min(CHUNK, n - t0);
+        const float* tab = tables + ((size_t)(req_chunk0[req] + c) * heads + head) * (2 * CHUNK * CHUNK + CHUNK);
+        __syncthreads();                      // the chunk before is done with the buffers (and S0 is whole)
+        {   // row t of every operand by the four threads that own row t of the products: all copies are in flight together
+            const int part = tid & 3;
+            const float* row = qkv + (size_t)(first + t0 + t) * channels;
+            const bool in = t < count;
+            if (vec) {
+                const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float* k4 = row + kvh * dk + g * dk;
+                const float* q4 = row + g * dk;
+                for (int r4 = part; r4 < dk / 4; r4 += 4) {
+                    if (in) { copy16(Ks + t * ld + 4 * r4, k4 + 4 * r4); copy16(Qs + t * ld + 4 * r4, q4 + 4 * r4); }
+                    else { *reinterpret_cast<float4*>(Ks + t * ld + 4 * r4) = zero; *reinterpret_cast<float4*>(Qs + t * ld + 4 * r4) = zero; }
+                }
+                // dv % 4 == 0: a group of four columns is whole or beyond the head
+                if (in && 4 * part < cols) copy16(Vs + t * CHUNK_COLS + 4 * part, row + 2 * kvh * dk + head * dv + col0 + 4 * part);
+                else *reinterpret_cast<float4*>(Vs + t * CHUNK_COLS + 4 * part) = zero;
+            } else {
+                for (int r = part; r < dk; r += 4) {
+                    Ks[t * ld + r] = in ? row[kvh * dk + g * dk + r] : 0.f;
+                    Qs[t * ld + r] = in ? row[g * dk + r] : 0.f;
+                }
+                for (int j = 4 * part; j < 4 * part + 4; ++j)
+                    Vs[t * CHUNK_COLS + j] = (in && j < cols) ? row[2 * kvh * dk + head * dv + col0 + j] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                copy16(Ts + t * lc_ + 4 * (part + 4 * k), tab + t * CHUNK + 4 * (part + 4 * k));
+                copy16(Ps + t * lc_ + 4 * (part + 4 * k), tab + CHUNK * CHUNK + t * CHUNK + 4 * (part + 4 * k));
+            }
+        }
+        if (tid < CHUNK) {
+            const float l = tab[2 * CHUNK * CHUNK + tid];
+            lg[tid] = l;
+            wl[tid] = expf(tab[2 * CHUNK * CHUNK + CHUNK - 1] - l);
+            bt[tid] = tid < count ? beta[(size_t)(first + t0 + tid) * heads + head] : 0.f;
+        }
+        copies_done();
+        __syncthreads();
+        // K S0 and Q S0, four columns of row t
+        float ks[4] = {0.f, 0.f, 0.f, 0.f}, qs[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int r = 0; r < dk; ++r) {
+            const float kt = Ks[t * ld + r], qt = Qs[t * ld + r];
+            const float4 s4 = *reinterpret_cast<const float4*>(S0 + r * CHUNK_COLS + j0);
+            ks[0] = fmaf(kt, s4.x, ks[0]); ks[1] = fmaf(kt, s4.y, ks[1]); ks[2] = fmaf(kt, s4.z, ks[2]); ks[3] = fmaf(kt, s4.w, ks[3]);
+            qs[0] = fmaf(qt, s4.x, qs[0]); qs[1] = fmaf(qt, s4.y, qs[1]); qs[2] = fmaf(qt, s4.z, qs[2]); qs[3] = fmaf(qt, s4.w, qs[3]);
+        }
+        const float ct = expf(lg[t]);
+        {
+            const float4 v4 = *reinterpret_cast<const float4*>(Vs + t * CHUNK_COLS + j0);
+            const float b = bt[t];
+            *reinterpret_cast<float4*>(Bs + t * CHUNK_COLS + j0) =
+                make_float4(b * (v4.x - ct * ks[0]), b * (v4.y - ct * ks[1]), b * (v4.z - ct * ks[2]), b * (v4.w - ct * ks[3]));
+        }
+        __syncthreads();
+        // U = T B (row t needs rows 0 .. t of B)
+        float u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int i = 0; i <= t; ++i) {
+            const float w = Ts[t * lc_ + i];
+            const float4 b4 = *reinterpret_cast<const float4*>(Bs + i * CHUNK_COLS + j0);
+            u[0] = fmaf(w, b4.x, u[0]); u[1] = fmaf(w, b4.y, u[1]); u[2] = fmaf(w, b4.z, u[2]); u[3] = fmaf(w, b4.w, u[3]);
+        }
+        __syncthreads();                      // every row of B has been read
+        *reinterpret_cast<float4*>(Bs + t * CHUNK_COLS + j0) = make_float4(u[0], u[1], u[2], u[3]);
+        __syncthreads();
+        // O = c_t Q S0 + P U
+        float o[4] = {ct * qs[0], ct * qs[1], ct * qs[2], ct * qs[3]};
+#pragma unroll 4
+        for (int i = 0; i <= t; ++i) {
+            const float w = Ps[t * lc_ + i];
+            const float4 u4 = *reinterpret_cast<const float4*>(Bs + i * CHUNK_COLS + j0);
+            o[0] = fmaf(w, u4.x, o[0]); o[1] = fmaf(w, u4.y, o[1]); o[2] = fmaf(w, u4.z, o[2]); o[3] = fmaf(w, u4.w, o[3]);
+        }
+        if (t < count) {
+            float* dst = out + ((size_t)(first + t0 + t) * heads + head) * dv + col0 + j0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (j0 + j < cols) dst[j] = o[j];
+        }
+        // S0 <- c_C S0 + sum_i (c_C / c_i) k_i u_i^T, four columns of rows t, t + 64, ...
+        const float last = lg[CHUNK - 1], cC = expf(last);
+        for (int r = t; r < dk; r += CHUNK) {
+            float4 s4 = *reinterpret_cast<const float4*>(S0 + r * CHUNK_COLS + j0);
+            s4.x *= cC; s4.y *= cC; s4.z *= cC; s4.w *= cC;
+#pragma unroll 4
+            for (int i = 0; i < count; ++i) {
+                const float w = wl[i] * Ks[i * ld + r];
+                const float4 u4 = *reinterpret_cast<const float4*>(Bs + i * CHUNK_COLS + j0);
+                s4.x = fmaf(w, u4.x, s4.x); s4.y = fmaf(w, u4.y, s4.y); s4.z = fmaf(w, u4.z, s4.z); s4.w = fmaf(w, u4.w, s4.w);
+            }
+            *reinterpret_cast<float4*>(S0 + r * CHUNK_COLS + j0) = s4;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < dk * CHUNK_COLS; i += CHUNK_THREADS) {
+        const int r = i / CHUNK_COLS, j = i - r * CHUNK_COLS;
+        if (j < cols) S[(size_t)r * dv + col0 + j] = S0[i];
+    }
+}
+
 template <typename OT>
 __global__ void __launch_bounds__(128)
 delta_output_kernel(const float* __restrict__ o, const float* __restrict__ proj, int row_stride, int gate_col,
@@ -276,7 +515,8 @@ CISR_EXPORT int cisr_delta_max_key_dim() { return 256; }
 
 CISR_EXPORT int cisr_delta_recurrence(const float* qkv, const float* beta, const float* decay, float* state, long long state_stride,
                                       const int* req_slot, const int* q_start, const int* q_len, float* out, int heads, int kvh,
-                                      int dk, int dv, int n_req, int lanes_per_column, void* stream) {
+                                      int dk, int dv, int n_req, int lanes_per_column, int below, void* stream) {
+    // `below` > 0: only requests that bring fewer tokens than that (the others run through cisr_delta_chunks)
     if (n_req <= 0) return 0;
     if (dk <= 0 || dk > 256 || dv <= 0 || heads % kvh) return -2;
     cudaStream_t s = (cudaStream_t)stream;
@@ -305,7 +545,7 @@ CISR_EXPORT int cisr_delta_recurrence(const float* qkv, const float* beta, const
             configured = smem;                                                                                            \
         }                                                                                                                 \
         return launch_kernel(delta_recurrence_kernel<R, L>, dim3(n_req, heads, (dv * L + DELTA_THREADS - 1) / DELTA_THREADS), dim3(DELTA_THREADS), smem, s, g_pdl, \
-                             qkv, beta, decay, state, state_stride, req_slot, q_start, q_len, out, heads, kvh, dk, dv);   \
+                             qkv, beta, decay, state, state_stride, req_slot, q_start, q_len, out, heads, kvh, dk, dv, below); \
     } while (0)
     const int rows = (dk + lanes - 1) / lanes;       // per lane
     if (lanes == 4) {
@@ -330,6 +570,42 @@ CISR_EXPORT int cisr_delta_recurrence(const float* qkv, const float* beta, const
     if (rows <= 4) CISR_DELTA(4, 32);
     CISR_DELTA(8, 32);
 #undef CISR_DELTA
+}
+
+CISR_EXPORT int cisr_delta_chunk_tokens() { return CHUNK; }
+CISR_EXPORT long long cisr_delta_chunk_table_floats() { return 2 * CHUNK * CHUNK + CHUNK; }
+
+// The recurrence for the requests of the step that bring at least `least` tokens, chunk by chunk.  chunk_req / chunk_t0:
+// per chunk its request and first token inside the portion; req_chunk0: per request the index of its first chunk (requests
+// below `least` have none); tables: float scratch [n_chunks][heads][cisr_delta_chunk_table_floats()].
+CISR_EXPORT int cisr_delta_chunks(const float* qkv, const float* beta, const float* decay, const int* chunk_req, const int* chunk_t0,
+                                  int n_chunks, const int* req_chunk0, float* tables, float* state, long long state_stride,
+                                  const int* req_slot, const int* q_start, const int* q_len, float* out, int heads, int kvh, int dk,
+                                  int dv, int n_req, int least, void* stream) {
+    if (n_chunks <= 0 || n_req <= 0) return 0;
+    if (dk <= 0 || dk > 256 || dv <= 0 || heads % kvh || least < 1) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem_tables = sizeof(float) * ((size_t)2 * CHUNK * (dk + 1) + 2 * CHUNK * (CHUNK + 1) + 2 * CHUNK);
+    const size_t smem_walk = sizeof(float) * ((size_t)2 * CHUNK * chunk_row_stride(dk) + 2 * CHUNK * (CHUNK + 4) + (size_t)dk * CHUNK_COLS +
+                                              2 * CHUNK * CHUNK_COLS + 3 * CHUNK);
+    if (smem_walk > 220 * 1024) return -3;
+    static size_t configured_tables = 48 * 1024, configured_walk = 48 * 1024;
+    if (smem_tables > configured_tables) {
+        cudaError_t e = cudaFuncSetAttribute(delta_chunk_tables_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tables);
+        if (e != cudaSuccess) return (int)e;
+        configured_tables = smem_tables;
+    }
+    if (smem_walk > configured_walk) {
+        cudaError_t e = cudaFuncSetAttribute(delta_chunk_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_walk);
+        if (e != cudaSuccess) return (int)e;
+        configured_walk = smem_walk;
+    }
+    int status = launch_kernel(delta_chunk_tables_kernel, dim3(n_chunks, heads), dim3(CHUNK_THREADS), smem_tables, s, g_pdl, qkv, beta, decay,
+                               chunk_req, chunk_t0, q_start, q_len, tables, heads, kvh, dk, dv);
+    if (status) return status;
+    return launch_kernel(delta_chunk_walk_kernel, dim3(n_req, heads, (dv + CHUNK_COLS - 1) / CHUNK_COLS), dim3(CHUNK_THREADS), smem_walk, s,
+                         g_pdl, qkv, beta, (const float*)tables, req_chunk0, state, state_stride, req_slot, q_start, q_len, out, heads,
+                         kvh, dk, dv, least);
 }
 
 CISR_EXPORT int cisr_delta_output(const float* o, const float* proj, int row_stride, int gate_col, const float* norm_w, float eps,

@@ -614,15 +614,20 @@ def bias_add(out: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
 # ------------------------------------------------------------------ the gated delta rule
 _delta_state = {}
 DELTA_MAX_KEY_DIM = 256
+DELTA_CHUNK = 64                                       # tokens per chunk of the chunked recurrence
+DELTA_CHUNK_TABLE = 2 * DELTA_CHUNK * DELTA_CHUNK + DELTA_CHUNK   # floats of scratch per (chunk, head)
 
 
 def _delta():
     lib = _delta_state.get("lib")
     if lib is None:
         lib = load_library("delta.cu")
-        for name in ("cisr_delta_prepare", "cisr_delta_keep", "cisr_delta_recurrence", "cisr_delta_output", "cisr_delta_max_key_dim"):
+        for name in ("cisr_delta_prepare", "cisr_delta_keep", "cisr_delta_recurrence", "cisr_delta_output", "cisr_delta_max_key_dim",
+                     "cisr_delta_chunks", "cisr_delta_chunk_tokens"):
             getattr(lib, name).restype = ctypes.c_int
-        assert lib.cisr_delta_max_key_dim() == DELTA_MAX_KEY_DIM
+        lib.cisr_delta_chunk_table_floats.restype = ctypes.c_longlong
+        assert lib.cisr_delta_max_key_dim() == DELTA_MAX_KEY_DIM and lib.cisr_delta_chunk_tokens() == DELTA_CHUNK
+        assert lib.cisr_delta_chunk_table_floats() == DELTA_CHUNK_TABLE
         lib.cisr_delta_set_pdl(int(_pdl_state["on"]))
         _delta_state["lib"] = lib
     return lib
@@ -647,12 +652,28 @@ def delta_keep(proj, state, req_slot, q_start, q_len, n_req, taps, channels, mat
                                     _p(req_slot), _p(q_start), _p(q_len), taps, channels, n_req, _stream()), "delta_keep")
 
 
-def delta_recurrence(qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim, lanes=0) -> None:
+def delta_chunks(qkv, beta, decay, chunk_req, chunk_t0, n_chunks, req_chunk0, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads,
+                 key_dim, value_dim, least) -> None:
+    """The recurrence for the requests that bring at least `least` tokens, a chunk of DELTA_CHUNK tokens at a time: two
+    launches (the chunks' tables, all at once; then the walk from chunk to chunk).  chunk_req, chunk_t0: per chunk its
+    request and its first token inside the portion; req_chunk0: per request the index of its first chunk."""
+    for name, t in (("chunk_req", chunk_req), ("chunk_t0", chunk_t0), ("req_chunk0", req_chunk0)):
+        _need(t, torch.int32, name, 1)
+    if chunk_req.numel() < n_chunks or chunk_t0.numel() < n_chunks or req_chunk0.numel() < n_req:
+        raise KernelError("delta_chunks: the chunk lists are too short")
+    tables = torch.empty((n_chunks, heads, DELTA_CHUNK_TABLE), dtype=torch.float32, device=qkv.device)
+    _check(_delta().cisr_delta_chunks(_p(qkv), _p(beta), _p(decay), _p(chunk_req), _p(chunk_t0), n_chunks, _p(req_chunk0), _p(tables),
+                                      _p(state), ctypes.c_longlong(state.shape[1]), _p(req_slot), _p(q_start), _p(q_len), _p(o), heads,
+                                      kv_heads, key_dim, value_dim, n_req, int(least), _stream()), "delta_chunks", own=2)
+
+
+def delta_recurrence(qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim, lanes=0, below=0) -> None:
     """The state's walk over each request's tokens, in order; o [tokens, heads, value_dim] float.  `lanes`: how many lanes
-    share a column of the state (4, 8, 16 or 32); 0: chosen by the size of the launch."""
+    share a column of the state (4, 8, 16 or 32); 0: chosen by the size of the launch.  `below` > 0: only the requests that
+    bring fewer tokens than that (the others are `delta_chunks`')."""
     _check(_delta().cisr_delta_recurrence(_p(qkv), _p(beta), _p(decay), _p(state), ctypes.c_longlong(state.shape[1]), _p(req_slot),
-                                          _p(q_start), _p(q_len), _p(o), heads, kv_heads, key_dim, value_dim, n_req, int(lanes), _stream()),
-           "delta_recurrence")
+                                          _p(q_start), _p(q_len), _p(o), heads, kv_heads, key_dim, value_dim, n_req, int(lanes), int(below),
+                                          _stream()), "delta_recurrence")
 
 
 def delta_output(o, proj, gate_col, norm_w, eps, out, heads, value_dim) -> None:
@@ -664,11 +685,13 @@ def delta_output(o, proj, gate_col, norm_w, eps, out, heads, value_dim) -> None:
 def delta_step(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
                norm_w: torch.Tensor, eps: float, norm_eps: float, token_req: torch.Tensor, req_slot: torch.Tensor, q_start: torch.Tensor,
                q_len: torch.Tensor, n_req: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, out: torch.Tensor,
-               lanes: int = 0) -> torch.Tensor:
+               lanes: int = 0, chunks=None) -> torch.Tensor:
     """The gated delta rule for a step's tokens (see csrc/delta.cu).  proj float [tokens, cols]: the stacked projection
     q | k | v | gate | b | a (cols may be padded beyond them); conv_w float [2 * kv_heads * key_dim + heads * value_dim, taps];
     state float [slots, heads * key_dim * value_dim + (taps - 1) * conv channels] is read and advanced for the step's
-    requests; out [tokens, >= heads * value_dim] in the operand type of the output projection."""
+    requests; out [tokens, >= heads * value_dim] in the operand type of the output projection.  `chunks`: None (every request
+    token by token) or (chunk_req, chunk_t0, req_chunk0, n_chunks, n_short, least): the requests with at least `least` tokens
+    run chunk by chunk, the `n_short` others token by token."""
     _need(proj, torch.float32, "proj", 2); _need(conv_w, torch.float32, "conv_w", 2); _need(state, torch.float32, "state", 2)
     for name, t in (("a_log", a_log), ("dt_bias", dt_bias), ("norm_w", norm_w)):
         _need(t, torch.float32, name, 1)
@@ -691,7 +714,14 @@ def delta_step(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch
                   value_dim, norm_eps)
     if taps > 1:
         delta_keep(proj, state, req_slot, q_start, q_len, n_req, taps, channels, matrix)
-    delta_recurrence(qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim, lanes)
+    if chunks is not None and chunks[3] > 0:
+        chunk_req, chunk_t0, req_chunk0, n_chunks, n_short, least = chunks
+        delta_chunks(qkv, beta, decay, chunk_req, chunk_t0, n_chunks, req_chunk0, state, req_slot, q_start, q_len, o, n_req, heads,
+                     kv_heads, key_dim, value_dim, least)
+        if n_short:
+            delta_recurrence(qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim, lanes, least)
+    else:
+        delta_recurrence(qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim, lanes)
     delta_output(o, proj, channels, norm_w, eps, out, heads, value_dim)
     return out
 
@@ -1421,7 +1451,9 @@ _DESCRIBE = {
     "activation": lambda x, out, kind: (int(x.shape[0]), int(x.shape[1])),
     "delta_prepare": lambda proj, conv_w, taps, *a: (int(proj.shape[0]), int(conv_w.shape[0]), int(taps)),
     "delta_keep": lambda proj, state, req_slot, q_start, q_len, n_req, taps, channels, matrix: (int(n_req), int(channels), int(taps)),
-    "delta_recurrence": lambda qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim, lanes=0:
+    "delta_chunks": lambda qkv, beta, decay, chunk_req, chunk_t0, n_chunks, req_chunk0, state, req_slot, q_start, q_len, o, n_req, heads,
+                           kv_heads, key_dim, value_dim, least: (int(qkv.shape[0]), int(n_req), int(heads), int(kv_heads), int(key_dim), int(value_dim)),
+    "delta_recurrence": lambda qkv, beta, decay, state, req_slot, q_start, q_len, o, n_req, heads, kv_heads, key_dim, value_dim, lanes=0, below=0:
         (int(qkv.shape[0]), int(n_req), int(heads), int(kv_heads), int(key_dim), int(value_dim)),
     "delta_output": lambda o, proj, *a: (int(o.shape[0]), int(o.shape[1] * o.shape[2])),
     "rope_store": lambda proj, *rest, **kw: (int(proj.shape[0]), int(proj.shape[1])),

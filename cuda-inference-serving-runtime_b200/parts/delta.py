@@ -9,7 +9,9 @@
 
 A request's state is S for every head and the last taps - 1 inputs of the convolution, float, in one row of a state
 tensor of the cache manager (`CacheUse("state", ...)`), zero when the request starts.  Portions of a prompt and single
-decoded tokens run the same kernels (`kernels.delta_step`), which walk a request's tokens in order.
+decoded tokens run the same kernels (`kernels.delta_step`).  Short portions and single tokens walk a request's tokens in
+order; portions of CHUNKED_FROM tokens and more run the chunked form of the same recurrence (csrc/delta.cu), which differs
+from the walk by rounding only.
 """
 from __future__ import annotations
 
@@ -22,6 +24,26 @@ from ..ops import kernels
 from .base import MIXERS, Mixer, TensorNeed, register
 from .feedforward import pad_columns
 from .linear import as_tensor, linear
+
+CHUNKED_FROM = kernels.DELTA_CHUNK       # portions of at least this many tokens run chunk by chunk
+DELTA_PLAN_KEY = ("delta_chunks", kernels.DELTA_CHUNK, CHUNKED_FROM)
+
+
+def chunk_plan(q_len):
+    """Which chunks the chunked recurrence runs for a step whose requests bring `q_len` tokens: per chunk its request and
+    its first token inside the portion, per request the index of its first chunk; and how many requests stay with the
+    token-by-token kernel.  Depends on the portion lengths alone, so steps of one shape share it."""
+    chunk_req, chunk_t0, req_chunk0, short = [], [], [], 0
+    for r, n in enumerate(q_len):
+        req_chunk0.append(len(chunk_req))
+        if n < CHUNKED_FROM:
+            short += 1
+            continue
+        for t0 in range(0, n, kernels.DELTA_CHUNK):
+            chunk_req.append(r)
+            chunk_t0.append(t0)
+    return chunk_req, chunk_t0, req_chunk0, short
+
 
 DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv", "beta": "b", "a": "a",
                  "a_log": "A_log", "dt_bias": "dt_bias", "gate": "g", "norm": "norm", "o": "o"}
@@ -89,13 +111,30 @@ class GatedDelta(Mixer):
     def cache_use(self) -> CacheUse:
         return CacheUse("state", state_shape=(self.state_size,), state_dtype="float32")
 
+    # ---------------------------------------------------------------- the launch plan of a step
+    def plan_key(self):
+        return DELTA_PLAN_KEY
+
+    def step_plan(self, host):
+        import numpy as np
+
+        from ..engine.batch import StepPlan
+        chunk_req, chunk_t0, req_chunk0, short = chunk_plan(host.q_len)
+        as_i32 = lambda values: np.asarray(values, dtype=np.int32)
+        return StepPlan(arrays={"chunk_req": as_i32(chunk_req), "chunk_t0": as_i32(chunk_t0), "req_chunk0": as_i32(req_chunk0)},
+                        info={"n_chunks": len(chunk_req), "n_short": short})
+
     def forward(self, h, ctx, cache):
         tokens = ctx.n_tokens
         proj = linear(as_tensor(h), self.w_in)                      # float [tokens, q | k | v | gate | b | a | padding]
         width = self.o.shape[1]
         make = torch.zeros if width != self.heads * self.value_dim else torch.empty
         out = make((tokens, width), dtype=self.dtype, device=ctx.device)
+        plan = ctx.plan_for(self)
+        chunks = None
+        if plan.info["n_chunks"]:
+            chunks = (plan["chunk_req"], plan["chunk_t0"], plan["req_chunk0"], plan.info["n_chunks"], plan.info["n_short"], CHUNKED_FROM)
         kernels.delta_step(proj, self.conv, self.taps, cache.state, self.a_log, self.dt_bias, self.norm, self.eps, UNIT_NORM_EPS,
                            ctx.token_req, ctx.req_slot, ctx.q_start, ctx.q_len, ctx.n_requests, self.heads, self.kvh, self.key_dim,
-                           self.value_dim, out)
+                           self.value_dim, out, chunks=chunks)
         return linear(out, self.o)

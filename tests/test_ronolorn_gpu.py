@@ -183,14 +183,17 @@ def test_attention_rows_kernel(dtype, from_keys, norm, interleaved, key_dim, val
     assert torch.equal(kernels.bias_add(y.clone(), b), y + b)
 
 
-@pytest.mark.parametrize("lanes", [0, 4, 8, 16, 32])
+@pytest.mark.parametrize("lanes, long", [(0, False), (4, False), (8, False), (16, False), (32, False), (0, True), (8, True)])
 @pytest.mark.parametrize("heads, kvh, dk, dv, taps", [(4, 2, 20, 24, 3), (2, 1, 32, 64, 4), (3, 3, 72, 40, 1), (1, 1, 130, 9, 2),
                                                        (2, 2, 128, 16, 5), (2, 1, 200, 8, 2), (1, 1, 256, 3, 2)])
-def test_delta_kernels_carry_their_state_across_portions(heads, kvh, dk, dv, taps, lanes):
+def test_delta_kernels_carry_their_state_across_portions(heads, kvh, dk, dv, taps, lanes, long):
     """The recurrence, the convolution with kept inputs, decay, beta, unit norms and the gated output norm against the
     plain mixer on whole sequences; two requests side by side in portions down to one token (shorter than the taps),
     one of them in a slot that held another request's state before; with every number of lanes per column of the state
-    that the recurrence kernel can be launched with (0: its own choice)."""
+    that the recurrence kernel can be launched with (0: its own choice).  `long`: portions of a chunk and more, which
+    run the chunked form (whole chunks, a chunk's tail, a chunk after single tokens) beside a request that stays with the
+    token-by-token kernel in the same step."""
+    from cisr_b200.parts.delta import CHUNKED_FROM, chunk_plan
     from cisr_b200.ops import kernels
     hidden, eps = 48, 1e-5
     g = torch.Generator().manual_seed(dk * 7 + dv)
@@ -203,7 +206,7 @@ def test_delta_kernels_carry_their_state_across_portions(heads, kvh, dk, dv, tap
          "g": torch.randn(heads * dv, hidden, generator=g) / 4, "norm": 1 + 0.1 * torch.randn(dv, generator=g),
          "o": torch.eye(heads * dv)}
     W64 = {k: v.to(F) for k, v in W.items()}
-    lengths = {0: 37, 1: 12}
+    lengths = {0: 237, 1: 140} if long else {0: 37, 1: 12}
     hs = {r: torch.randn(n, hidden, generator=g) for r, n in lengths.items()}
     want = {r: pr.mixer_delta(h.to(F), W64, "", m, eps) for r, h in hs.items()}
     stacked = torch.cat([W[k] for k in ("q", "k", "v", "g", "b", "a")]).to(F)
@@ -213,7 +216,7 @@ def test_delta_kernels_carry_their_state_across_portions(heads, kvh, dk, dv, tap
     slot = {0: 2, 1: 0}
     for s in slot.values():
         state[s].zero_()                          # what the cache manager does when a request takes a slot
-    cuts = {0: [5, 1, 1, 2, 9, 1, 18], 1: [1, 1, 3, 7]}
+    cuts = {0: [70, 1, 64, 2, 100], 1: [1, 3, 129, 7]} if long else {0: [5, 1, 1, 2, 9, 1, 18], 1: [1, 1, 3, 7]}
     at = {0: 0, 1: 0}
     got = {0: [], 1: []}
     while any(cuts.values()):
@@ -225,9 +228,11 @@ def test_delta_kernels_carry_their_state_across_portions(heads, kvh, dk, dv, tap
         token_req = np.concatenate([np.full(n, i, dtype=np.int32) for i, n in enumerate(sizes)])
         out = torch.empty((rows.shape[0], heads * dv), dtype=torch.float32, device="cuda")
         dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).cuda()
+        chunk_req, chunk_t0, req_chunk0, short = chunk_plan(sizes)
+        chunks = (dev(chunk_req), dev(chunk_t0), dev(req_chunk0), len(chunk_req), short, CHUNKED_FROM) if chunk_req else None
         kernels.delta_step(proj, conv, taps, state, W["A_log"].cuda(), W["dt_bias"].cuda(), W["norm"].cuda(), eps, 1e-6,
                            dev(token_req), dev([slot[r] for r in batch]), dev(q_start), dev(sizes), len(batch), heads, kvh, dk, dv, out,
-                           lanes=lanes)
+                           lanes=lanes, chunks=chunks)
         for i, (r, n) in enumerate(zip(batch, sizes)):
             got[r].append(out[q_start[i]:q_start[i] + n].cpu())
             at[r] += n
