@@ -475,7 +475,7 @@ KERNEL_KIND = {   # which kernels of the two designs are alike
     "latent_values": "product per head", "moe_select": "row kernels", "moe_gather": "row kernels",
     "moe_combine": "row kernels", "moe_sort": "bookkeeping", "stream_add": "row kernels", "swiglu": "row kernels",
     "hyper_mix_norm": "norm", "attention_rows": "row kernels", "activation": "row kernels", "delta_prepare": "row kernels",
-    "delta_output": "row kernels", "delta_keep": "bookkeeping", "delta_recurrence": "recurrence"}
+    "delta_output": "row kernels", "delta_keep": "bookkeeping", "delta_recurrence": "recurrence", "delta_chunks": "recurrence"}
 
 
 def generic_need(name: str, shape: tuple, cache_tokens: int, causal: int):
@@ -525,6 +525,12 @@ def generic_need(name: str, shape: tuple, cache_tokens: int, causal: int):
         return tokens * channels * 8, 2.0 * tokens * channels * taps
     if name == "delta_output":
         return shape[0] * shape[1] * 10, 0.0
+    if name == "delta_chunks":
+        # as the token-by-token walk, plus the chunks' tables written once and read once per 16 value columns
+        tokens, n_req, heads, kvh, dk, dv = shape
+        chunks = (tokens + 63) // 64
+        return (n_req * 2 * heads * dk * dv + tokens * (2 * kvh * dk + 2 * heads * dv + 2 * heads)
+                + chunks * heads * (2 * 64 * 64 + 64) * (1 + (dv + 15) // 16)) * 4, 0.0
     if name == "delta_recurrence":
         # the state once in and once out per request, the tokens' operands once; the arithmetic runs on the CUDA cores in float
         # (seven operations per state element and token), which the tensor-core peak does not describe: bytes only

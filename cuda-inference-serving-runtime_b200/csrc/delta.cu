@@ -230,7 +230,7 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
 //     A[t][i] = beta_t (c_t / c_i) (k_t . k_i)              (i < t)
 // so with T = (I + A)^-1 (lower triangular, ones on the diagonal) and P[t][i] = (c_t / c_i) (q_t . k_i) (i <= t):
 //     U = T B,   B[t] = beta_t (v_t - c_t (K S0)[t]);   O[t] = c_t (Q S0)[t] + (P U)[t];   S_C = c_C S0 + sum_i (c_C / c_i) k_i u_i^T.
-// T and P depend on no state: `delta_chunk_tables` makes them for every chunk of the step at once, a CTA per (chunk, head).
+// T and P depend on no state: `delta_chunk_tables` makes them for every chunk of the step at once, a CTA per (chunk, key head).
 // `delta_chunk_walk` then carries the state from chunk to chunk, a CTA per (request, head, CHUNK_COLS value columns), with
 // small matrix products in shared memory instead of a chain of shuffles per token.  Ratios of decays are taken as
 // exp(l_t - l_i) from sums of logarithms (t >= i: never above one; a decay of zero is floored at e^-80).  Float throughout.
@@ -240,20 +240,27 @@ __host__ __device__ inline int chunk_row_stride(int dk) { return dk % 4 == 0 ? d
 __global__ void __launch_bounds__(CHUNK_THREADS)
 delta_chunk_tables_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
                           const int* __restrict__ chunk_req, const int* __restrict__ chunk_t0, const int* __restrict__ q_start,
-                          const int* __restrict__ q_len, float* __restrict__ tables, int heads, int kvh, int dk, int dv) {
+                          const int* __restrict__ q_len, float* __restrict__ tables, int heads, int kvh, int dk, int dv,
+                          int heads_per_cta) {
+    // A CTA per (chunk, `heads_per_cta` heads of one key head): the products k_t . k_i and q_t . k_i are the same for every
+    // head of a group and are made once per CTA (4 x 4 tiles per thread, tiles above the diagonal skipped); then, head by
+    // head, the decays and beta turn them into A and P, and A is inverted.  The host gives a CTA the whole group when the
+    // launch has CTAs to spare, and one head when it has not (the heads' turns in a CTA run one after the other).
     extern __shared__ float sm[];
     const int ld = dk + 1, lc_ = CHUNK + 1;
     float* Ks = sm;                           // [CHUNK][dk + 1]
     float* Qs = Ks + CHUNK * ld;              // [CHUNK][dk + 1]
-    float* As = Qs + CHUNK * ld;              // [CHUNK][CHUNK + 1]
+    float* Gk = Qs + CHUNK * ld;              // [CHUNK][CHUNK + 1]: k_t . k_i
+    float* Gq = Gk + CHUNK * lc_;             // [CHUNK][CHUNK + 1]: q_t . k_i
+    float* As = Gq + CHUNK * lc_;             // [CHUNK][CHUNK + 1]
     float* Ts = As + CHUNK * lc_;             // [CHUNK][CHUNK + 1]
     float* lg = Ts + CHUNK * lc_;             // [CHUNK] sums of log decays
     float* bt = lg + CHUNK;                   // [CHUNK] beta
     pdl_trigger();
-    const int chunk = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const int chunk = blockIdx.x, head0 = blockIdx.y * heads_per_cta, tid = threadIdx.x;
     const int req = chunk_req[chunk], t0 = chunk_t0[chunk];
     const int count = min(CHUNK, q_len[req] - t0), first = q_start[req] + t0;
-    const int g = head / (heads / kvh), channels = 2 * kvh * dk + heads * dv;
+    const int g = head0 / (heads / kvh), channels = 2 * kvh * dk + heads * dv;
     pdl_wait();
     {
         const int t = tid >> 2;
@@ -263,60 +270,79 @@ delta_chunk_tables_kernel(const float* __restrict__ qkv, const float* __restrict
             Qs[t * ld + r] = t < count ? row[g * dk + r] : 0.f;
         }
     }
-    if (tid < CHUNK) {
-        bt[tid] = tid < count ? beta[(size_t)(first + tid) * heads + head] : 0.f;
-        lg[tid] = tid < count ? fmaxf(logf(decay[(size_t)(first + tid) * heads + head]), -80.f) : 0.f;
-    }
     __syncthreads();
-    if (tid == 0) {                           // the running sum, in token order
-        float sum = 0.f;
-        for (int t = 0; t < CHUNK; ++t) { sum += lg[t]; lg[t] = sum; }
-    }
-    __syncthreads();
-    // 16 entries of row t per thread: A below the diagonal, P on and below it
-    float* out_T = tables + ((size_t)chunk * heads + head) * (2 * CHUNK * CHUNK + CHUNK);
-    float* out_P = out_T + CHUNK * CHUNK;
     {
-        const int t = tid >> 2, i0 = (tid & 3) * 16;
-        float kk[16], qk[16];
+        const int t4 = (tid >> 4) * 4, i4 = (tid & 15) * 4;
+        float kk[4][4], qk[4][4];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) { kk[j] = 0.f; qk[j] = 0.f; }
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) { kk[a][b] = 0.f; qk[a][b] = 0.f; }
+        if (i4 <= t4) {
 #pragma unroll 2
-        for (int r = 0; r < dk; ++r) {
-            const float kt = Ks[t * ld + r], qt = Qs[t * ld + r];
+            for (int r = 0; r < dk; ++r) {
+                float kt[4], qt[4], ki[4];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float ki = Ks[(i0 + j) * ld + r];
-                kk[j] = fmaf(kt, ki, kk[j]);
-                qk[j] = fmaf(qt, ki, qk[j]);
+                for (int a = 0; a < 4; ++a) { kt[a] = Ks[(t4 + a) * ld + r]; qt[a] = Qs[(t4 + a) * ld + r]; ki[a] = Ks[(i4 + a) * ld + r]; }
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) { kk[a][b] = fmaf(kt[a], ki[b], kk[a][b]); qk[a][b] = fmaf(qt[a], ki[b], qk[a][b]); }
             }
         }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int i = i0 + j;
-            const float ratio = i <= t ? expf(lg[t] - lg[i]) : 0.f;
-            As[t * lc_ + i] = i < t ? bt[t] * ratio * kk[j] : 0.f;
-            out_P[t * CHUNK + i] = ratio * qk[j];
-        }
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) { Gk[(t4 + a) * lc_ + i4 + b] = kk[a][b]; Gq[(t4 + a) * lc_ + i4 + b] = qk[a][b]; }
     }
-    if (tid < CHUNK) out_T[2 * CHUNK * CHUNK + tid] = lg[tid];
-    __syncthreads();
-    // T = (I + A)^-1 by forward substitution: T[t][c] = [t == c] - sum_{c <= i < t} A[t][i] T[i][c].  Four neighbouring
-    // lanes own column c and take every fourth i; a row is finished by two shuffles before the next row reads it.
-    {
-        const int c = tid >> 2, p = tid & 3;
-        for (int t = 0; t < CHUNK; ++t) {
-            float a = 0.f;
+    for (int hd = 0; hd < heads_per_cta; ++hd) {
+        const int head = head0 + hd;
+        float* out_T = tables + ((size_t)chunk * heads + head) * (2 * CHUNK * CHUNK + CHUNK);
+        float* out_P = out_T + CHUNK * CHUNK;
+        __syncthreads();                      // the products are whole; the head before is done with A, T, lg
+        if (tid < CHUNK) {
+            bt[tid] = tid < count ? beta[(size_t)(first + tid) * heads + head] : 0.f;
+            lg[tid] = tid < count ? fmaxf(logf(decay[(size_t)(first + tid) * heads + head]), -80.f) : 0.f;
+        }
+        __syncthreads();
+        if (tid == 0) {                       // the running sum, in token order
+            float sum = 0.f;
+            for (int t = 0; t < CHUNK; ++t) { sum += lg[t]; lg[t] = sum; }
+        }
+        __syncthreads();
+        {
+            const int t = tid >> 2, i0 = (tid & 3) * 16;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int i = i0 + j;
+                const float ratio = i <= t ? expf(lg[t] - lg[i]) : 0.f;
+                As[t * lc_ + i] = i < t ? bt[t] * ratio * Gk[t * lc_ + i] : 0.f;
+                out_P[t * CHUNK + i] = ratio * Gq[t * lc_ + i];
+            }
+        }
+        if (tid < CHUNK) out_T[2 * CHUNK * CHUNK + tid] = lg[tid];
+        __syncthreads();
+        // T = (I + A)^-1 by forward substitution: T[t][c] = [t == c] - sum_{c <= i < t} A[t][i] T[i][c].  Four neighbouring
+        // lanes own column c and take every fourth i; a row is finished by two shuffles before the next row reads it.
+        {
+            const int c = tid >> 2, p = tid & 3;
+            for (int t = 0; t < CHUNK; ++t) {
+                float a = 0.f;
 #pragma unroll 4
-            for (int i = c + p; i < t; i += 4) a = fmaf(-As[t * lc_ + i], Ts[i * lc_ + c], a);
-            a += __shfl_xor_sync(0xffffffffu, a, 1);
-            a += __shfl_xor_sync(0xffffffffu, a, 2);
-            if (p == 0) Ts[t * lc_ + c] = t < c ? 0.f : (t == c ? 1.f : 0.f) + a;
-            __syncwarp();
+                for (int i = c + p; i < t; i += 4) a = fmaf(-As[t * lc_ + i], Ts[i * lc_ + c], a);
+                a += __shfl_xor_sync(0xffffffffu, a, 1);
+                a += __shfl_xor_sync(0xffffffffu, a, 2);
+                if (p == 0) Ts[t * lc_ + c] = t < c ? 0.f : (t == c ? 1.f : 0.f) + a;
+                __syncwarp();
+            }
+        }
+        __syncthreads();
+        {
+            const int t = tid >> 2, i0 = (tid & 3) * 16;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) out_T[t * CHUNK + i0 + j] = Ts[t * lc_ + i0 + j];
         }
     }
-    __syncthreads();
-    for (int i = tid; i < CHUNK * CHUNK; i += CHUNK_THREADS) out_T[i] = Ts[(i / CHUNK) * lc_ + (i % CHUNK)];
 }
 
 __global__ void __launch_bounds__(CHUNK_THREADS)
@@ -585,7 +611,7 @@ CISR_EXPORT int cisr_delta_chunks(const float* qkv, const float* beta, const flo
     if (n_chunks <= 0 || n_req <= 0) return 0;
     if (dk <= 0 || dk > 256 || dv <= 0 || heads % kvh || least < 1) return -2;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem_tables = sizeof(float) * ((size_t)2 * CHUNK * (dk + 1) + 2 * CHUNK * (CHUNK + 1) + 2 * CHUNK);
+    const size_t smem_tables = sizeof(float) * ((size_t)2 * CHUNK * (dk + 1) + 4 * CHUNK * (CHUNK + 1) + 2 * CHUNK);
     const size_t smem_walk = sizeof(float) * ((size_t)2 * CHUNK * chunk_row_stride(dk) + 2 * CHUNK * (CHUNK + 4) + (size_t)dk * CHUNK_COLS +
                                               2 * CHUNK * CHUNK_COLS + 3 * CHUNK);
     if (smem_walk > 220 * 1024) return -3;
@@ -600,8 +626,14 @@ CISR_EXPORT int cisr_delta_chunks(const float* qkv, const float* beta, const flo
         if (e != cudaSuccess) return (int)e;
         configured_walk = smem_walk;
     }
-    int status = launch_kernel(delta_chunk_tables_kernel, dim3(n_chunks, heads), dim3(CHUNK_THREADS), smem_tables, s, g_pdl, qkv, beta, decay,
-                               chunk_req, chunk_t0, q_start, q_len, tables, heads, kvh, dk, dv);
+    static int sms = 0;
+    if (!sms) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 148;
+    }
+    const int per_cta = (long long)n_chunks * heads >= 4ll * sms ? heads / kvh : 1;
+    int status = launch_kernel(delta_chunk_tables_kernel, dim3(n_chunks, heads / per_cta), dim3(CHUNK_THREADS), smem_tables, s, g_pdl, qkv, beta,
+                               decay, chunk_req, chunk_t0, q_start, q_len, tables, heads, kvh, dk, dv, per_cta);
     if (status) return status;
     return launch_kernel(delta_chunk_walk_kernel, dim3(n_req, heads, (dv + CHUNK_COLS - 1) / CHUNK_COLS), dim3(CHUNK_THREADS), smem_walk, s,
                          g_pdl, qkv, beta, (const float*)tables, req_chunk0, state, state_stride, req_slot, q_start, q_len, out, heads,
