@@ -121,3 +121,24 @@ def test_plain_window_edges():
     ok = pr.visible(6, 3)
     assert ok[5].tolist() == [False, False, False, True, True, True] and ok[1].tolist() == [True, True, False, False, False, False]
     assert pr.visible(4, None)[3].all() and pr.visible(4, 1).sum() == 4
+
+
+def test_chunk_plan_of_the_delta_rule():
+    """Portions of a chunk and more are cut into chunks (the last may be short); shorter ones and single tokens have none
+    and are counted for the token-by-token kernel; every request knows where its chunks start."""
+    from cisr_b200.parts.delta import CHUNKED_FROM, chunk_plan
+    assert CHUNKED_FROM == 64
+    chunk_req, chunk_t0, req_chunk0, short = chunk_plan([130, 1, 64, 63, 200])
+    assert chunk_req == [0, 0, 0, 2, 4, 4, 4, 4] and chunk_t0 == [0, 64, 128, 0, 0, 64, 128, 192]
+    assert req_chunk0 == [0, 3, 3, 4, 4] and short == 2
+    assert chunk_plan([1, 1, 1]) == ([], [], [0, 0, 0], 3)
+
+
+def test_the_delta_mixer_plans_with_the_step():
+    from cisr_b200.engine.batch import HostBatch
+    model = Model(spec_of(rm.RA), "float32", config=rm.RA, device=None)
+    keys = {type(p).__name__: p.plan_key() for p in model.planners()}
+    assert set(keys) == {"WindowedAttention", "GatedDelta"}          # one plan per key, whatever the number of layers
+    delta = [p for p in model.planners() if type(p).__name__ == "GatedDelta"][0]
+    plan = delta.step_plan(HostBatch(["a", "b"], [0, 1], [0, 70], [70, 1], [70, 9], 71, []))
+    assert plan.info == {"n_chunks": 2, "n_short": 1} and plan.arrays["chunk_t0"].tolist() == [0, 64]
