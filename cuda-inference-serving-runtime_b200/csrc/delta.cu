@@ -231,10 +231,10 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
 // so with T = (I + A)^-1 (lower triangular, ones on the diagonal) and P[t][i] = (c_t / c_i) (q_t . k_i) (i <= t):
 //     U = T B,   B[t] = beta_t (v_t - c_t (K S0)[t]);   O[t] = c_t (Q S0)[t] + (P U)[t];   S_C = c_C S0 + sum_i (c_C / c_i) k_i u_i^T.
 // T and P depend on no state: `delta_chunk_tables` makes them for every chunk of the step at once, a CTA per (chunk, key head).
-// `delta_chunk_walk` then carries the state from chunk to chunk, a CTA per (request, head, CHUNK_COLS value columns), with
+// `delta_chunk_walk` then carries the state from chunk to chunk, a CTA per (request, head, 16 or 8 value columns), with
 // small matrix products in shared memory instead of a chain of shuffles per token.  Ratios of decays are taken as
 // exp(l_t - l_i) from sums of logarithms (t >= i: never above one; a decay of zero is floored at e^-80).  Float throughout.
-constexpr int CHUNK = 64, CHUNK_COLS = 16, CHUNK_THREADS = 256;
+constexpr int CHUNK = 64, CHUNK_THREADS = 256;
 __host__ __device__ inline int chunk_row_stride(int dk) { return dk % 4 == 0 ? dk + 4 : dk + 1; }
 
 __global__ void __launch_bounds__(CHUNK_THREADS)
@@ -345,7 +345,9 @@ delta_chunk_tables_kernel(const float* __restrict__ qkv, const float* __restrict
     }
 }
 
-__global__ void __launch_bounds__(CHUNK_THREADS)
+// COLS value columns per CTA (16, or 8 where that many CTAs would not fill the device): 64 rows x COLS / 4 threads
+template <int COLS>
+__global__ void __launch_bounds__(CHUNK * COLS / 4)
 delta_chunk_walk_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ tables,
                         const int* __restrict__ req_chunk0, float* __restrict__ state, long long state_stride,
                         const int* __restrict__ req_slot, const int* __restrict__ q_start, const int* __restrict__ q_len,
@@ -359,58 +361,59 @@ delta_chunk_walk_kernel(const float* __restrict__ qkv, const float* __restrict__
     float* Qs = Ks + CHUNK * ld;              // [CHUNK][ld]
     float* Ts = Qs + CHUNK * ld;              // [CHUNK][CHUNK + 4]
     float* Ps = Ts + CHUNK * lc_;             // [CHUNK][CHUNK + 4]
-    float* S0 = Ps + CHUNK * lc_;             // [dk][CHUNK_COLS]
-    float* Bs = S0 + dk * CHUNK_COLS;         // [CHUNK][CHUNK_COLS]: B, then U
-    float* Vs = Bs + CHUNK * CHUNK_COLS;      // [CHUNK][CHUNK_COLS]
-    float* lg = Vs + CHUNK * CHUNK_COLS;      // [CHUNK]
+    float* S0 = Ps + CHUNK * lc_;             // [dk][COLS]
+    float* Bs = S0 + dk * COLS;         // [CHUNK][COLS]: B, then U
+    float* Vs = Bs + CHUNK * COLS;      // [CHUNK][COLS]
+    float* lg = Vs + CHUNK * COLS;      // [CHUNK]
     float* bt = lg + CHUNK;                   // [CHUNK]
     float* wl = bt + CHUNK;                   // [CHUNK]: c_C / c_i
     pdl_trigger();
+    constexpr int PARTS = COLS / 4, THREADS = CHUNK * PARTS;      // threads per row, threads per CTA
     const int req = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
     const int n = q_len[req];
-    const int col0 = blockIdx.z * CHUNK_COLS, cols = min(CHUNK_COLS, dv - col0);
+    const int col0 = blockIdx.z * COLS, cols = min(COLS, dv - col0);
     const int g = head / (heads / kvh), channels = 2 * kvh * dk + heads * dv;
     const int first = q_start[req];
     float* S = state + (size_t)req_slot[req] * state_stride + (size_t)head * dk * dv;
     pdl_wait();
     if (n < least) return;                    // short portions and single tokens are the token-by-token kernel's
-    for (int i = tid; i < dk * CHUNK_COLS; i += CHUNK_THREADS) {
-        const int r = i / CHUNK_COLS, j = i - r * CHUNK_COLS;
+    for (int i = tid; i < dk * COLS; i += THREADS) {
+        const int r = i / COLS, j = i - r * COLS;
         S0[i] = j < cols ? S[(size_t)r * dv + col0 + j] : 0.f;
     }
-    const int t = tid >> 2, j0 = (tid & 3) * 4;        // this thread's four entries of every [CHUNK][CHUNK_COLS] product
+    const int t = tid / PARTS, j0 = (tid % PARTS) * 4;     // this thread's four entries of every [CHUNK][COLS] product
     const int n_chunks = (n + CHUNK - 1) / CHUNK;
     for (int c = 0; c < n_chunks; ++c) {
         const int t0 = c * CHUNK, count = min(CHUNK, n - t0);
         const float* tab = tables + ((size_t)(req_chunk0[req] + c) * heads + head) * (2 * CHUNK * CHUNK + CHUNK);
         __syncthreads();                      // the chunk before is done with the buffers (and S0 is whole)
         {   // row t of every operand by the four threads that own row t of the products: all copies are in flight together
-            const int part = tid & 3;
+            const int part = tid % PARTS;
             const float* row = qkv + (size_t)(first + t0 + t) * channels;
             const bool in = t < count;
             if (vec) {
                 const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
                 const float* k4 = row + kvh * dk + g * dk;
                 const float* q4 = row + g * dk;
-                for (int r4 = part; r4 < dk / 4; r4 += 4) {
+                for (int r4 = part; r4 < dk / 4; r4 += PARTS) {
                     if (in) { copy16(Ks + t * ld + 4 * r4, k4 + 4 * r4); copy16(Qs + t * ld + 4 * r4, q4 + 4 * r4); }
                     else { *reinterpret_cast<float4*>(Ks + t * ld + 4 * r4) = zero; *reinterpret_cast<float4*>(Qs + t * ld + 4 * r4) = zero; }
                 }
                 // dv % 4 == 0: a group of four columns is whole or beyond the head
-                if (in && 4 * part < cols) copy16(Vs + t * CHUNK_COLS + 4 * part, row + 2 * kvh * dk + head * dv + col0 + 4 * part);
-                else *reinterpret_cast<float4*>(Vs + t * CHUNK_COLS + 4 * part) = zero;
+                if (in && 4 * part < cols) copy16(Vs + t * COLS + 4 * part, row + 2 * kvh * dk + head * dv + col0 + 4 * part);
+                else *reinterpret_cast<float4*>(Vs + t * COLS + 4 * part) = zero;
             } else {
-                for (int r = part; r < dk; r += 4) {
+                for (int r = part; r < dk; r += PARTS) {
                     Ks[t * ld + r] = in ? row[kvh * dk + g * dk + r] : 0.f;
                     Qs[t * ld + r] = in ? row[g * dk + r] : 0.f;
                 }
                 for (int j = 4 * part; j < 4 * part + 4; ++j)
-                    Vs[t * CHUNK_COLS + j] = (in && j < cols) ? row[2 * kvh * dk + head * dv + col0 + j] : 0.f;
+                    Vs[t * COLS + j] = (in && j < cols) ? row[2 * kvh * dk + head * dv + col0 + j] : 0.f;
             }
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                copy16(Ts + t * lc_ + 4 * (part + 4 * k), tab + t * CHUNK + 4 * (part + 4 * k));
-                copy16(Ps + t * lc_ + 4 * (part + 4 * k), tab + CHUNK * CHUNK + t * CHUNK + 4 * (part + 4 * k));
+            for (int k = part; k < CHUNK / 4; k += PARTS) {
+                copy16(Ts + t * lc_ + 4 * k, tab + t * CHUNK + 4 * k);
+                copy16(Ps + t * lc_ + 4 * k, tab + CHUNK * CHUNK + t * CHUNK + 4 * k);
             }
         }
         if (tid < CHUNK) {
@@ -426,15 +429,15 @@ delta_chunk_walk_kernel(const float* __restrict__ qkv, const float* __restrict__
 #pragma unroll 4
         for (int r = 0; r < dk; ++r) {
             const float kt = Ks[t * ld + r], qt = Qs[t * ld + r];
-            const float4 s4 = *reinterpret_cast<const float4*>(S0 + r * CHUNK_COLS + j0);
+            const float4 s4 = *reinterpret_cast<const float4*>(S0 + r * COLS + j0);
             ks[0] = fmaf(kt, s4.x, ks[0]); ks[1] = fmaf(kt, s4.y, ks[1]); ks[2] = fmaf(kt, s4.z, ks[2]); ks[3] = fmaf(kt, s4.w, ks[3]);
             qs[0] = fmaf(qt, s4.x, qs[0]); qs[1] = fmaf(qt, s4.y, qs[1]); qs[2] = fmaf(qt, s4.z, qs[2]); qs[3] = fmaf(qt, s4.w, qs[3]);
         }
         const float ct = expf(lg[t]);
         {
-            const float4 v4 = *reinterpret_cast<const float4*>(Vs + t * CHUNK_COLS + j0);
+            const float4 v4 = *reinterpret_cast<const float4*>(Vs + t * COLS + j0);
             const float b = bt[t];
-            *reinterpret_cast<float4*>(Bs + t * CHUNK_COLS + j0) =
+            *reinterpret_cast<float4*>(Bs + t * COLS + j0) =
                 make_float4(b * (v4.x - ct * ks[0]), b * (v4.y - ct * ks[1]), b * (v4.z - ct * ks[2]), b * (v4.w - ct * ks[3]));
         }
         __syncthreads();
@@ -443,18 +446,18 @@ delta_chunk_walk_kernel(const float* __restrict__ qkv, const float* __restrict__
 #pragma unroll 4
         for (int i = 0; i <= t; ++i) {
             const float w = Ts[t * lc_ + i];
-            const float4 b4 = *reinterpret_cast<const float4*>(Bs + i * CHUNK_COLS + j0);
+            const float4 b4 = *reinterpret_cast<const float4*>(Bs + i * COLS + j0);
             u[0] = fmaf(w, b4.x, u[0]); u[1] = fmaf(w, b4.y, u[1]); u[2] = fmaf(w, b4.z, u[2]); u[3] = fmaf(w, b4.w, u[3]);
         }
         __syncthreads();                      // every row of B has been read
-        *reinterpret_cast<float4*>(Bs + t * CHUNK_COLS + j0) = make_float4(u[0], u[1], u[2], u[3]);
+        *reinterpret_cast<float4*>(Bs + t * COLS + j0) = make_float4(u[0], u[1], u[2], u[3]);
         __syncthreads();
         // O = c_t Q S0 + P U
         float o[4] = {ct * qs[0], ct * qs[1], ct * qs[2], ct * qs[3]};
 #pragma unroll 4
         for (int i = 0; i <= t; ++i) {
             const float w = Ps[t * lc_ + i];
-            const float4 u4 = *reinterpret_cast<const float4*>(Bs + i * CHUNK_COLS + j0);
+            const float4 u4 = *reinterpret_cast<const float4*>(Bs + i * COLS + j0);
             o[0] = fmaf(w, u4.x, o[0]); o[1] = fmaf(w, u4.y, o[1]); o[2] = fmaf(w, u4.z, o[2]); o[3] = fmaf(w, u4.w, o[3]);
         }
         if (t < count) {
@@ -466,20 +469,20 @@ delta_chunk_walk_kernel(const float* __restrict__ qkv, const float* __restrict__
         // S0 <- c_C S0 + sum_i (c_C / c_i) k_i u_i^T, four columns of rows t, t + 64, ...
         const float last = lg[CHUNK - 1], cC = expf(last);
         for (int r = t; r < dk; r += CHUNK) {
-            float4 s4 = *reinterpret_cast<const float4*>(S0 + r * CHUNK_COLS + j0);
+            float4 s4 = *reinterpret_cast<const float4*>(S0 + r * COLS + j0);
             s4.x *= cC; s4.y *= cC; s4.z *= cC; s4.w *= cC;
 #pragma unroll 4
             for (int i = 0; i < count; ++i) {
                 const float w = wl[i] * Ks[i * ld + r];
-                const float4 u4 = *reinterpret_cast<const float4*>(Bs + i * CHUNK_COLS + j0);
+                const float4 u4 = *reinterpret_cast<const float4*>(Bs + i * COLS + j0);
                 s4.x = fmaf(w, u4.x, s4.x); s4.y = fmaf(w, u4.y, s4.y); s4.z = fmaf(w, u4.z, s4.z); s4.w = fmaf(w, u4.w, s4.w);
             }
-            *reinterpret_cast<float4*>(S0 + r * CHUNK_COLS + j0) = s4;
+            *reinterpret_cast<float4*>(S0 + r * COLS + j0) = s4;
         }
     }
     __syncthreads();
-    for (int i = tid; i < dk * CHUNK_COLS; i += CHUNK_THREADS) {
-        const int r = i / CHUNK_COLS, j = i - r * CHUNK_COLS;
+    for (int i = tid; i < dk * COLS; i += THREADS) {
+        const int r = i / COLS, j = i - r * COLS;
         if (j < cols) S[(size_t)r * dv + col0 + j] = S0[i];
     }
 }
@@ -612,8 +615,8 @@ CISR_EXPORT int cisr_delta_chunks(const float* qkv, const float* beta, const flo
     if (dk <= 0 || dk > 256 || dv <= 0 || heads % kvh || least < 1) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem_tables = sizeof(float) * ((size_t)2 * CHUNK * (dk + 1) + 4 * CHUNK * (CHUNK + 1) + 2 * CHUNK);
-    const size_t smem_walk = sizeof(float) * ((size_t)2 * CHUNK * chunk_row_stride(dk) + 2 * CHUNK * (CHUNK + 4) + (size_t)dk * CHUNK_COLS +
-                                              2 * CHUNK * CHUNK_COLS + 3 * CHUNK);
+    const size_t smem_walk = sizeof(float) * ((size_t)2 * CHUNK * chunk_row_stride(dk) + 2 * CHUNK * (CHUNK + 4) + (size_t)dk * 16 +
+                                              2 * CHUNK * 16 + 3 * CHUNK);        // sized for 16 columns, also where a CTA takes 8
     if (smem_walk > 220 * 1024) return -3;
     static size_t configured_tables = 48 * 1024, configured_walk = 48 * 1024;
     if (smem_tables > configured_tables) {
@@ -622,7 +625,8 @@ CISR_EXPORT int cisr_delta_chunks(const float* qkv, const float* beta, const flo
         configured_tables = smem_tables;
     }
     if (smem_walk > configured_walk) {
-        cudaError_t e = cudaFuncSetAttribute(delta_chunk_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_walk);
+        cudaError_t e = cudaFuncSetAttribute(delta_chunk_walk_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_walk);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(delta_chunk_walk_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_walk);
         if (e != cudaSuccess) return (int)e;
         configured_walk = smem_walk;
     }
@@ -635,9 +639,13 @@ CISR_EXPORT int cisr_delta_chunks(const float* qkv, const float* beta, const flo
     int status = launch_kernel(delta_chunk_tables_kernel, dim3(n_chunks, heads / per_cta), dim3(CHUNK_THREADS), smem_tables, s, g_pdl, qkv, beta,
                                decay, chunk_req, chunk_t0, q_start, q_len, tables, heads, kvh, dk, dv, per_cta);
     if (status) return status;
-    return launch_kernel(delta_chunk_walk_kernel, dim3(n_req, heads, (dv + CHUNK_COLS - 1) / CHUNK_COLS), dim3(CHUNK_THREADS), smem_walk, s,
-                         g_pdl, qkv, beta, (const float*)tables, req_chunk0, state, state_stride, req_slot, q_start, q_len, out, heads,
-                         kvh, dk, dv, least);
+    // 16 value columns per CTA, or 8 where that would leave more than half of the SMs without a CTA (measured: with 128
+    // CTAs of 16 columns on 148 SMs, splitting them made the launch slower; with 64 it made it faster)
+    if (2ll * n_req * heads * ((dv + 15) / 16) > sms)
+        return launch_kernel(delta_chunk_walk_kernel<16>, dim3(n_req, heads, (dv + 15) / 16), dim3(CHUNK * 4), smem_walk, s, g_pdl, qkv, beta,
+                             (const float*)tables, req_chunk0, state, state_stride, req_slot, q_start, q_len, out, heads, kvh, dk, dv, least);
+    return launch_kernel(delta_chunk_walk_kernel<8>, dim3(n_req, heads, (dv + 7) / 8), dim3(CHUNK * 2), smem_walk, s, g_pdl, qkv, beta,
+                         (const float*)tables, req_chunk0, state, state_stride, req_slot, q_start, q_len, out, heads, kvh, dk, dv, least);
 }
 
 CISR_EXPORT int cisr_delta_output(const float* o, const float* proj, int row_stride, int gate_col, const float* norm_w, float eps,
