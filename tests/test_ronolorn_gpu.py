@@ -434,6 +434,36 @@ def test_sharp_attention_depends_on_single_keys(tmp_path_factory):
         compare(replay.run_steps(stepper_for(model, steps), steps), requests, reference, "float32", scale=8.0)
 
 
+def test_repeated_step_shapes_replay_from_graphs_with_state_and_chunks(tmp_path_factory):
+    """Portions of the same lengths recur: from the second time on the step is a graph replay.  The portions are long
+    enough for the chunked recurrence (its chunk lists travel with the graph's metadata) and pass the windows; single
+    tokens beside them take the token-by-token kernel in the same captured step.  The warm-up run in front of a capture
+    must not advance any request's recurrent state twice."""
+    from cisr_b200 import StepEntry, Stepper
+    cfg, weights, path, model, _, _ = setup("ra", "float32", tmp_path_factory)
+    stepper = Stepper(model, n_pages=60, page_size=16, max_slots=4, graph=True)
+    tokens = {k: rm.random_tokens(cfg, 231, 20 + i) for i, k in enumerate("abcd")}
+    reference = {k: plain(cfg, weights, t) for k, t in tokens.items()}
+    got = {}
+    for k in "abcd":
+        stepper.create(k)
+    plan = [[("a", 0, 100)], [("b", 0, 100)], [("c", 0, 100)], [("d", 0, 100)], [("a", 100, 100)],
+            [("b", 100, 70), ("a", 200, 1)], [("c", 100, 70), ("a", 201, 1)], [("d", 100, 70), ("b", 170, 1)],
+            [("a", 202, 1), ("b", 171, 1)], [("a", 203, 1), ("b", 172, 1)], [("a", 204, 1), ("b", 173, 1)]]
+    for step in plan:
+        entries = [StepEntry(k, tokens[k][at:at + n], [n - 1, 0] if n > 1 else [0]) for k, at, n in step]
+        logits = stepper.step(entries).cpu().numpy()
+        row = 0
+        for k, at, n in step:
+            for w in ([n - 1, 0] if n > 1 else [0]):
+                got[(k, at + w)] = logits[row].copy()
+                row += 1
+        stepper.cache.check()
+    compare(got, tokens, reference, "float32", scale=4.0)
+    report = stepper.graphs.report()
+    assert report["shape_entries"] >= 2 and report["hits"] >= 4
+
+
 # ------------------------------------------------------------------ generation through the scheduler and the command line
 @pytest.mark.parametrize("case, graph", [("ra", False), ("ra", True), ("rc", False)])
 def test_greedy_generation_through_the_scheduler(case, graph, tmp_path_factory):
