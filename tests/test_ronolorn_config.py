@@ -81,7 +81,7 @@ def test_refusals_come_before_any_weight_is_read(change, message):
         architecture_for(cfg).config_class.from_dict(cfg)
 
 
-@pytest.mark.parametrize("rot", [{"base": 70000.0, "dims": 32, "scaling": rm.YARN}, {"base": 500000.0, "dims": 48,
+@pytest.mark.parametrize("rot", [{"base": 70000.0, "dims": 32, "scaling": rm.YARN}, {"base": 400000.0, "dims": 40,
                                   "scaling": {"factor": 16.0, "original": 1024, "fast": 24.0, "slow": 2.0}},
                                  {"base": 100.0, "dims": 6, "scaling": {"factor": 1.5, "original": 8, "fast": 1.0, "slow": 1.0}}])
 def test_stretched_frequencies_match_the_plain_ones(rot):
