@@ -334,6 +334,22 @@ def test_sizes_that_are_no_multiples_of_eight(dtype, tmp_path):
         compare(replay.run_steps(stepper_for(model, steps, slack_pages=2), steps), requests, reference, dtype, scale=4.0)
 
 
+@pytest.mark.parametrize("kinds", [("delta", "delta"), ("attention_2",), ("attention", "attention")])
+def test_models_of_one_kind_of_mixer(kinds, tmp_path):
+    """Only recurrent layers (no pages at all, state slots alone), only attention (no state): the cache manager, the
+    launch plans and the trace of mixed steps must not count on the other kind being there."""
+    mixers = {"delta": rm.delta(2, 1, 24, 20, 3), "attention": rm.attention(2, 1, 24, 20, 0.2, window=11, rot={"base": 800.0, "dims": 10}),
+              "attention_2": rm.attention(3, 1, 32, 32, 0.2, window=13, rot={"base": 800.0, "dims": 32})}
+    cfg = {"architecture": "Ronolorn", "vocab": 61, "width": 48, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-5}, "streams": 2,
+           "layers": [rm.layer(k, mixers[k], 40 if i == 0 else None) for i, k in enumerate(kinds)]}
+    weights = rm.make_weights(cfg, 3)
+    model = model_of(cfg, weights, tmp_path)
+    requests = {"m": rm.random_tokens(cfg, 90, 1), "n": rm.random_tokens(cfg, 30, 2), "o": rm.random_tokens(cfg, 5, 3)}
+    reference = {k: plain(cfg, weights, t) for k, t in requests.items()}
+    for steps in (replay.trace_whole(requests), replay.trace_mixed(requests, seed=4, max_live=3)):
+        compare(replay.run_steps(stepper_for(model, steps, slack_pages=2), steps), requests, reference, "float32", scale=4.0)
+
+
 def test_a_request_alone_and_in_a_crowd(tmp_path_factory):
     """The same request by itself and beside three others of other lengths, portion by portion and token by token:
     float32 logits agree far inside the comparison's bound (the products may choose another kernel by the step's
